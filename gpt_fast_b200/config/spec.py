@@ -38,10 +38,12 @@ class ScheduleEntry:
     named by several entries: its weights are then shared).  `cache` is the id
     of the cache entry the run's mixer uses; with `owns_cache=False` the run
     appends nothing and reads what the entry's owner wrote earlier in the
-    same step."""
+    same step.  `kv_from` (or None) is the id of another entry whose keys and values the run's mixer reads in place
+    of keys and values of its own, while per-sequence state (if the mixer keeps any) stays in its own entry `cache`."""
     layer: int
     cache: int
     owns_cache: bool = True
+    kv_from: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -75,3 +77,5 @@ class ModelSpec:
                 owners[e.cache] = i
             elif e.cache not in owners:
                 raise ValueError(f"schedule[{i}] reads cache entry {e.cache} before any run wrote it")
+            if e.kv_from is not None and (e.kv_from not in owners or owners[e.kv_from] >= i):
+                raise ValueError(f"schedule[{i}] reads the keys and values of entry {e.kv_from} before any run wrote them")

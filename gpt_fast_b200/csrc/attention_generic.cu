@@ -9,7 +9,10 @@
 // sees only keys of its own block of `chunk` positions, blocks counted from
 // position 0 of the sequence), `sink` (one number per query head whose
 // exponential joins the softmax denominator without a value), a value head
-// size `dv` of its own, and values that are the leading part of the key rows.
+// size `dv` of its own, values that are the leading part of the key rows, and a
+// bias on the scaled score that depends on head and distance n = p - j only:
+// `bias` (a table [bias_len][H], row min(n, bias_len - 1), added) and `slopes`
+// (one number per head, slopes[h] * n taken off).
 //
 // One block per (token, query head).  Keys are visited in chunks of 128 that
 // start at multiples of 128 of the ABSOLUTE position, with an online softmax
@@ -28,7 +31,8 @@ template <typename T>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedKV kv, GfbBatch b,
                          int H, int G, int d, int dv, int v_row, float scale, int window, int chunk,
-                         const float* __restrict__ sink, int* status) {
+                         const float* __restrict__ sink, const float* __restrict__ bias, int bias_len,
+                         const float* __restrict__ slopes, int* status) {
     extern __shared__ float smem[];
     float* qs = smem;              // [d]
     float* ps = smem + d;          // [CHUNK]
@@ -79,6 +83,8 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
             float dot = 0.f;
             for (int i = 0; i < d; i++) dot = fmaf(qs[i], gfb_to_f32(krow[i]), dot);
             sc = dot;
+            if (bias != nullptr) sc += bias[(size_t)min(pos - j, bias_len - 1) * H + h];
+            if (slopes != nullptr) sc -= slopes[h] * (float)(pos - j);
         }
         float m_new = fmaxf(m_run, gfb_block_max(sc, scratch));
         float p = live ? expf(sc - m_new) : 0.f;
@@ -127,12 +133,14 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
                                   int n_pages,
                                   const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
                                   int n_seqs, int n_tokens, int H, int G, int d, int dv, float scale, int window,
-                                  int chunk, const float* sink, int values_in_keys, int* status, cudaStream_t stream) {
+                                  int chunk, const float* sink, int values_in_keys, const float* bias, int bias_len,
+                                  const float* slopes, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dv <= 0) dv = d;
     if (dv > CHUNK * MAX_DPT) return gfb_fail("gfb_attention_generic: value head size %d exceeds %d", dv, CHUNK * MAX_DPT);
     if (G <= 0 || H % G) return gfb_fail("gfb_attention_generic: %d heads do not divide into %d groups", H, G);
     if (H > 65535) return gfb_fail("gfb_attention_generic: %d heads exceed the grid limit", H);
+    if (bias != nullptr && bias_len < 1) return gfb_fail("gfb_attention_generic: a distance table of %d rows", bias_len);
     // values_in_keys: a value is the first dv dimensions of its key row (a latent shared by keys and values), so
     // the value pool is the key pool read with the keys' row stride
     if (values_in_keys && dv > d) return gfb_fail("gfb_attention_generic: values of %d dimensions inside keys of %d", dv, d);
@@ -144,10 +152,10 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream,
-                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, status);
+                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, status);
     else if (dt == GFB_F32)
         e = gfb_launch(attention_generic_kernel<float>, grid, dim3(CHUNK), smem, stream,
-                       (const float*)q, (float*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, status);
+                       (const float*)q, (float*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, status);
     else
         return gfb_fail("gfb_attention_generic: unknown type %d", dt);
     return gfb_check(e, "gfb_attention_generic");

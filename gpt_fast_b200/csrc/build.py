@@ -38,6 +38,7 @@ LIBRARIES = {
     "embedding": (["embedding.cu"], [], []),
     "latent": (["latent.cu"], [], []),
     "recurrent": (["recurrent.cu"], [], []),
+    "moe": (["moe.cu"], [], []),
 }
 HEADERS = ["common.cuh", "attn_decode_noalloc.h"]
 

@@ -6,6 +6,9 @@
 // step's first token is per-sequence state: prev[slot], written by a second small kernel behind the
 // first (the last token of every sequence of the step), so that a sequence may arrive in any portions.
 // The sum is 32-bit.
+//
+// And token embedding plus a learned vector per position: out[t] = table[tok_t] * scale + positions[p_t], p_t the
+// token's place in its sequence.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -69,4 +72,47 @@ GFB_API int gfb_embed_hashed(const int* tokens, const void* table, const void* e
     if (gfb_check(e, "gfb_embed_hashed")) return 1;
     e = gfb_launch(embed_prev_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, stream, tokens, b, prev);
     return gfb_check(e, "gfb_embed_hashed (previous token)");
+}
+
+template <typename TW>
+__global__ void embed_positions_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, const TW* __restrict__ positions,
+                                       float* __restrict__ out, GfbBatch b, int D, int V, int P, float scale, int* status) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    const int s = b.tok_seq[t];
+    const int pos = b.lengths[b.slots[s]] + (t - b.cu_seqlens[s]);
+    float* o = out + (size_t)t * D;
+    const bool bad_id = id < 0 || id >= V, bad_pos = pos < 0 || pos >= P;
+    if (bad_id || bad_pos) {
+        if (threadIdx.x == 0) {
+            if (bad_id) gfb_report(status, GFB_ERR_TOKEN_RANGE, t, id);
+            else gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        }
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const TW* e = table + (size_t)id * D;
+    const TW* x = positions + (size_t)pos * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_to_f32(e[i]) * scale + gfb_to_f32(x[i]);
+}
+
+// tokens int32 [T]; table [V, D] and positions [P, D] of type table_dt; out float32 [T, D].
+GFB_API int gfb_embed_positions(const int* tokens, const void* table, const void* positions, int table_dt, float* out,
+                                const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths, int n_seqs,
+                                int n_tokens, int D, int V, int P, float scale, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    const int threads = D >= 1024 ? 256 : 128;
+    cudaError_t e;
+    if (table_dt == GFB_BF16)
+        e = gfb_launch(embed_positions_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table,
+                       (const __nv_bfloat16*)positions, out, b, D, V, P, scale, status);
+    else if (table_dt == GFB_F32)
+        e = gfb_launch(embed_positions_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table,
+                       (const float*)positions, out, b, D, V, P, scale, status);
+    else
+        return gfb_fail("gfb_embed_positions: unknown table type %d", table_dt);
+    return gfb_check(e, "gfb_embed_positions");
 }

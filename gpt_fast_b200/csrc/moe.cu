@@ -1,0 +1,403 @@
+// Mixture of experts: a router that picks `top` of E small gated feed-forwards per token, and the experts.
+//
+// gfb_moe_route         from 32-bit router logits: s = sigmoid(z); the `top` experts with the largest s + correction
+//                       (lowest index on ties); weights s / (sum of the chosen s + 1e-20) * scale
+// gfb_moe_glu           act[pair, f] = g * sigmoid(alpha g) * (u + shift),  g = min(gate_f . h, limit),
+//                       u = clamp(up_f . h, -limit, limit), for every (token, chosen expert) pair
+// gfb_moe_down          x[t] += sum over the token's chosen experts of weight * (W_down act[pair]); 32-bit sum into the stream
+//
+// The gate and up rows of an expert alternate in one matrix w13 [E, 2F, D], the down matrix is w2 [E, D, F].
+// A pair is p = t * top + r (r: rank of the expert among the token's choices).
+//
+// Two forms of the expert products.  Few tokens (a decode step): a warp per output number streams the weight row once,
+// 16 bytes per lane and load, the token's input staged in shared memory.  Many tokens (a prompt): the pairs are sorted by
+// expert (gfb_moe_plan: each expert's rows padded to whole tiles) and the products run tile by tile, each tile with its
+// expert's weights (gfb_moe_glu_tiles, gfb_moe_down_tiles), the rows' results scattered back to pair order.  In both
+// forms a number is one ascending sum over k in 32-bit (per lane and then a fixed butterfly, or per thread), so a token's
+// result does not depend on what else is in the batch.
+#include "common.cuh"
+
+GFB_DEFINE_LAST_ERROR()
+
+__device__ __forceinline__ float ldw(const void* p, int dt, size_t i) {
+    return dt == GFB_BF16 ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------ router ----
+constexpr int MAX_EPL = 16;           // experts per lane: E <= 512
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_kernel(const float* __restrict__ logits, int ld, const void* __restrict__ correction, int c_dt, int E, int top,
+                 float scale, int* __restrict__ idx, float* __restrict__ weights, int T) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
+    if (t >= T) return;
+    float s[MAX_EPL], c[MAX_EPL];
+#pragma unroll
+    for (int i = 0; i < MAX_EPL; i++) {
+        const int e = lane + 32 * i;
+        if (e < E) {
+            s[i] = sigmoid_f(logits[(size_t)t * ld + e]);
+            c[i] = s[i] + (correction != nullptr ? ldw(correction, c_dt, e) : 0.f);
+        } else {
+            s[i] = 0.f;
+            c[i] = -INFINITY;
+        }
+    }
+    float sum = 0.f, mine = 0.f;       // lane r keeps the r-th chosen score
+    int mine_e = 0;
+    for (int r = 0; r < top; r++) {
+        float best = -INFINITY, best_s = 0.f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; i++)
+            if (c[i] > best) { best = c[i]; best_e = lane + 32 * i; best_s = s[i]; }     // ascending e per lane: the lowest index wins a tie
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, best_s, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; i++)
+            if (lane + 32 * i == best_e) c[i] = -INFINITY;
+        sum += best_s;
+        if (lane == r) { mine = best_s; mine_e = best_e; }
+    }
+    if (lane < top) {
+        idx[(size_t)t * top + lane] = mine_e;
+        weights[(size_t)t * top + lane] = mine / (sum + 1e-20f) * scale;
+    }
+}
+
+GFB_API int gfb_moe_route(const float* logits, int ld, const void* correction, int c_dt, int E, int top, float scale, int* idx,
+                          float* weights, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || E > 32 * MAX_EPL) return gfb_fail("gfb_moe_route: %d experts (1 to %d)", E, 32 * MAX_EPL);
+    if (top < 1 || top > 32 || top > E) return gfb_fail("gfb_moe_route: %d of %d experts per token (1 to 32)", top, E);
+    cudaError_t e = gfb_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(32 * ROUTE_WARPS), 0, stream, logits, ld,
+                               correction, c_dt, E, top, scale, idx, weights, T);
+    return gfb_check(e, "gfb_moe_route");
+}
+
+// ------------------------------------------------------------------------------------ few tokens ----
+// dot of a weight row with a staged 32-bit vector: lanes take 16 bytes of the row at a time where the row allows it
+template <typename T> struct Vec;
+template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
+template <> struct Vec<float> { static constexpr int N = 4; };
+
+template <typename T>
+__device__ __forceinline__ float row_dot(const T* __restrict__ row, const float* __restrict__ v, int n, int lane, bool wide) {
+    float acc = 0.f;
+    if (wide) {
+        constexpr int N = Vec<T>::N;
+        for (int c = lane * N; c < n; c += 32 * N) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < N; i++) acc = fmaf(gfb_to_f32(e[i]), v[c + i], acc);
+        }
+    } else {
+        for (int c = lane; c < n; c += 32) acc = fmaf(gfb_to_f32(row[c]), v[c], acc);
+    }
+    return gfb_warp_sum(acc);
+}
+
+template <typename T>
+__device__ __forceinline__ bool rows_wide(const T* base, int n) {
+    return n % Vec<T>::N == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+
+constexpr int GEMV_WARPS = 8;
+constexpr int GLU_PER_WARP = 2;       // hidden units per warp: 4 weight rows in flight
+
+template <typename T>
+__global__ void __launch_bounds__(32 * GEMV_WARPS)
+moe_glu_gemv_kernel(const T* __restrict__ h, const int* __restrict__ idx, const T* __restrict__ w13, T* __restrict__ act, int top,
+                    int E, int F, int D, float limit, float alpha, float shift) {
+    extern __shared__ __align__(16) float hs[];
+    gfb_pdl_launch();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pair = blockIdx.y, t = pair / top;
+    gfb_pdl_wait();
+    const int e = idx[pair];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hs[i] = gfb_to_f32(h[(size_t)t * D + i]);
+    __syncthreads();
+    if (e < 0 || e >= E) return;
+    const T* w = w13 + (size_t)e * 2 * F * D;
+    const bool wide = rows_wide(w, D);
+    const int f0 = (blockIdx.x * GEMV_WARPS + warp) * GLU_PER_WARP;
+#pragma unroll
+    for (int r = 0; r < GLU_PER_WARP; r++) {
+        const int f = f0 + r;
+        if (f >= F) break;
+        float g = row_dot(w + (size_t)(2 * f) * D, hs, D, lane, wide);
+        float u = row_dot(w + (size_t)(2 * f + 1) * D, hs, D, lane, wide);
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        if (lane == 0) act[(size_t)pair * F + f] = gfb_from_f32<T>(g * sigmoid_f(alpha * g) * (u + shift));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * GEMV_WARPS)
+moe_down_gemv_kernel(const T* __restrict__ act, const int* __restrict__ idx, const float* __restrict__ weights, const T* __restrict__ w2,
+                     float* __restrict__ x, int top, int E, int F, int D) {
+    extern __shared__ __align__(16) float as[];        // [top][F]
+    gfb_pdl_launch();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.y;
+    gfb_pdl_wait();
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = gfb_to_f32(act[(size_t)t * top * F + i]);
+    __syncthreads();
+    const int n = blockIdx.x * GEMV_WARPS + warp;
+    if (n >= D) return;
+    const bool wide = rows_wide(w2, F) && ((size_t)D * F) % Vec<T>::N == 0;
+    float acc = 0.f;
+    for (int r = 0; r < top; r++) {
+        const int e = idx[(size_t)t * top + r];
+        if (e < 0 || e >= E) continue;
+        acc = fmaf(weights[(size_t)t * top + r], row_dot(w2 + ((size_t)e * D + n) * F, as + (size_t)r * F, F, lane, wide), acc);
+    }
+    if (lane == 0) x[(size_t)t * D + n] += acc;
+}
+
+template <typename K>
+static int allow_smem(K kernel, size_t smem, const char* what) {
+    if (smem > 200 * 1024) return gfb_fail("%s: %zu bytes of shared memory", what, smem);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("%s: %s", what, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------ many tokens ----
+// The plan: rows of the sorted order.  Expert e's pairs take rows start[e] .. start[e] + count[e] - 1, start[e] a
+// multiple of the tile height BM; row_pair[row] is the pair of a row (-1: padding), tile_expert[tile] the expert whose
+// weights a tile of that many rows uses (-1: the tile is beyond the last expert's rows).  One block builds it; the order of an
+// expert's rows among themselves is whatever the atomics give, and no result depends on it.
+constexpr int PLAN_THREADS = 1024;
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, int* __restrict__ row_pair, int* __restrict__ pair_row,
+                int* __restrict__ tile_expert, int max_tiles) {
+    extern __shared__ int sh[];          // count[E], start[E], fill[E]
+    int* count = sh;
+    int* start = sh + E;
+    int* fill = sh + 2 * E;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
+    for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) row_pair[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; e++) {
+            start[e] = at;
+            const int tiles = (count[e] + tile_rows - 1) / tile_rows;
+            for (int i = 0; i < tiles; i++) tile_expert[at / tile_rows + i] = e;
+            at += tiles * tile_rows;
+        }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) {
+            const int row = start[e] + atomicAdd(&fill[e], 1);
+            row_pair[row] = p;
+            pair_row[p] = row;
+        } else {
+            pair_row[p] = -1;
+        }
+    }
+}
+
+GFB_API int gfb_moe_plan(const int* idx, int n_pairs, int E, int tile_rows, int* row_pair, int* pair_row, int* tile_expert, int max_tiles,
+                         cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    const long busy = n_pairs < E ? n_pairs : E;             // experts that can have rows at all
+    if (tile_rows < 1 || (long)max_tiles < ((long)n_pairs + busy * (tile_rows - 1)) / tile_rows)
+        return gfb_fail("gfb_moe_plan: %d tiles of %d rows cannot hold %d pairs of %d experts", max_tiles, tile_rows, n_pairs, E);
+    const size_t smem = (size_t)3 * E * sizeof(int);
+    cudaError_t e = gfb_launch(moe_plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, stream, idx, n_pairs, E, tile_rows, row_pair, pair_row,
+                               tile_expert, max_tiles);
+    return gfb_check(e, "gfb_moe_plan");
+}
+
+// Tiles on CUDA cores (the 32-bit path, and bfloat16 shapes the tensor-core tiles do not take): 64 x 64 outputs per block,
+// each one thread's ascending sum over k.  GLU: A = h rows gathered by pair / top, W = w13 of the tile's expert, the
+// output act[row, n / 2] from the gate (even n) and up (odd n) columns.  DOWN: A = act rows (sorted order), W = w2 of
+// the tile's expert, the output y[pair, n] in 32-bit, pair order.
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_tiles_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ C, const int* __restrict__ row_pair,
+                      const int* __restrict__ tile_expert, int top, int N, int K, float limit, float alpha, float shift) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int src_row[BM];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (threadIdx.x < BM) {
+        const int p = row_pair[m0 + threadIdx.x];
+        src_row[threadIdx.x] = p < 0 ? -1 : (GLU ? p / top : m0 + threadIdx.x);
+    }
+    __syncthreads();
+    const T* We = W + (size_t)e * N * K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int el = threadIdx.x + i * 256;
+            const int r = el >> 4, k = el & 15;
+            const int gk = k0 + k, gn = n0 + r, sr = src_row[r];
+            As[k][r] = (sr >= 0 && gk < K) ? gfb_to_f32(A[(size_t)sr * K + gk]) : 0.f;
+            Ws[k][r] = (gn < N && gk < K) ? gfb_to_f32(We[(size_t)gn * K + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = ty * 4 + i;
+        const int p = row_pair[m0 + r];
+        if (p < 0) continue;
+        if (GLU) {
+            T* out = (T*)C + (size_t)(m0 + r) * (N >> 1);
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < N) {
+                    float g = acc[i][j], u = acc[i][j + 1];
+                    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+                    out[n >> 1] = gfb_from_f32<T>(g * sigmoid_f(alpha * g) * (u + shift));
+                }
+            }
+        } else {
+            float* out = (float*)C + (size_t)p * N;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int n = n0 + tx * 4 + j;
+                if (n < N) out[n] = acc[i][j];
+            }
+        }
+    }
+}
+
+// x[t] += sum_r weights[t, r] * y[t * top + r] in ascending r
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, float* __restrict__ x, int top,
+                                   int D, long n) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long t = i / D;
+    const int c = (int)(i - t * D);
+    float acc = 0.f;
+    for (int r = 0; r < top; r++) acc = fmaf(weights[t * top + r], y[((size_t)t * top + r) * D + c], acc);
+    x[i] += acc;
+}
+
+// h [T, D], w13 [E, 2F, D], act [rows, F] of type dt.  tiles = 0: the few-token form, act in pair order (rows = T * top);
+// otherwise act in the plan's sorted order (rows = max_tiles * 64) and row_pair, tile_expert from gfb_moe_plan with tiles of 64 rows.
+GFB_API int gfb_moe_glu(const void* h, const int* idx, const void* w13, void* act, int dt, int T, int top, int E, int F, int D,
+                        float limit, float alpha, float shift, const int* row_pair, const int* tile_expert, int max_tiles,
+                        cudaStream_t stream) {
+    if (T <= 0) return 0;
+    typedef __nv_bfloat16 bf16;
+    cudaError_t e;
+    if (max_tiles > 0) {
+        dim3 grid((2 * F + BN - 1) / BN, max_tiles);
+        if (max_tiles > 65535) return gfb_fail("gfb_moe_glu: %d tiles exceed the grid limit", max_tiles);
+        if (dt == GFB_BF16)
+            e = gfb_launch(moe_tiles_simt_kernel<bf16, true>, grid, dim3(256), 0, stream, (const bf16*)h, (const bf16*)w13, act, row_pair,
+                           tile_expert, top, 2 * F, D, limit, alpha, shift);
+        else if (dt == GFB_F32)
+            e = gfb_launch(moe_tiles_simt_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)h, (const float*)w13, act, row_pair,
+                           tile_expert, top, 2 * F, D, limit, alpha, shift);
+        else return gfb_fail("gfb_moe_glu: unknown type %d", dt);
+        return gfb_check(e, "gfb_moe_glu (tiles)");
+    }
+    const long pairs = (long)T * top;
+    if (pairs > 65535) return gfb_fail("gfb_moe_glu: %ld pairs exceed the grid limit of the few-token form", pairs);
+    const size_t smem = (size_t)D * sizeof(float);
+    dim3 grid((F + GEMV_WARPS * GLU_PER_WARP - 1) / (GEMV_WARPS * GLU_PER_WARP), (unsigned)pairs);
+    if (dt == GFB_BF16) {
+        if (allow_smem(moe_glu_gemv_kernel<bf16>, smem, "gfb_moe_glu")) return 1;
+        e = gfb_launch(moe_glu_gemv_kernel<bf16>, grid, dim3(32 * GEMV_WARPS), smem, stream, (const bf16*)h, idx, (const bf16*)w13, (bf16*)act,
+                       top, E, F, D, limit, alpha, shift);
+    } else if (dt == GFB_F32) {
+        if (allow_smem(moe_glu_gemv_kernel<float>, smem, "gfb_moe_glu")) return 1;
+        e = gfb_launch(moe_glu_gemv_kernel<float>, grid, dim3(32 * GEMV_WARPS), smem, stream, (const float*)h, idx, (const float*)w13,
+                       (float*)act, top, E, F, D, limit, alpha, shift);
+    } else return gfb_fail("gfb_moe_glu: unknown type %d", dt);
+    return gfb_check(e, "gfb_moe_glu");
+}
+
+// act as gfb_moe_glu left it; w2 [E, D, F]; x float32 [T, D] += the weighted sum of the chosen experts' outputs.
+// With tiles: y float32 [T * top, D] is scratch for the experts' outputs in pair order.
+GFB_API int gfb_moe_down(const void* act, const int* idx, const float* weights, const void* w2, float* x, int dt, int T, int top,
+                         int E, int F, int D, const int* row_pair, const int* tile_expert, int max_tiles, float* y,
+                         cudaStream_t stream) {
+    if (T <= 0) return 0;
+    typedef __nv_bfloat16 bf16;
+    cudaError_t e;
+    if (max_tiles > 0) {
+        dim3 grid((D + BN - 1) / BN, max_tiles);
+        if (dt == GFB_BF16)
+            e = gfb_launch(moe_tiles_simt_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16*)act, (const bf16*)w2, (void*)y,
+                           row_pair, tile_expert, top, D, F, 0.f, 0.f, 0.f);
+        else if (dt == GFB_F32)
+            e = gfb_launch(moe_tiles_simt_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)act, (const float*)w2, (void*)y,
+                           row_pair, tile_expert, top, D, F, 0.f, 0.f, 0.f);
+        else return gfb_fail("gfb_moe_down: unknown type %d", dt);
+        if (gfb_check(e, "gfb_moe_down (tiles)")) return 1;
+        const long n = (long)T * D;
+        e = gfb_launch(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)y, weights, x, top, D, n);
+        return gfb_check(e, "gfb_moe_down (combine)");
+    }
+    if (T > 65535) return gfb_fail("gfb_moe_down: %d tokens exceed the grid limit of the few-token form", T);
+    const size_t smem = (size_t)top * F * sizeof(float);
+    dim3 grid((D + GEMV_WARPS - 1) / GEMV_WARPS, T);
+    if (dt == GFB_BF16) {
+        if (allow_smem(moe_down_gemv_kernel<bf16>, smem, "gfb_moe_down")) return 1;
+        e = gfb_launch(moe_down_gemv_kernel<bf16>, grid, dim3(32 * GEMV_WARPS), smem, stream, (const bf16*)act, idx, weights, (const bf16*)w2,
+                       x, top, E, F, D);
+    } else if (dt == GFB_F32) {
+        if (allow_smem(moe_down_gemv_kernel<float>, smem, "gfb_moe_down")) return 1;
+        e = gfb_launch(moe_down_gemv_kernel<float>, grid, dim3(32 * GEMV_WARPS), smem, stream, (const float*)act, idx, weights,
+                       (const float*)w2, x, top, E, F, D);
+    } else return gfb_fail("gfb_moe_down: unknown type %d", dt);
+    return gfb_check(e, "gfb_moe_down");
+}

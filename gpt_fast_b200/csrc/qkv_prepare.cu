@@ -1,7 +1,8 @@
 // What happens to q, k and v between their projection and the attention, for mixers that the
 // rotate-and-append kernel of core.cu does not cover: any subset of
 //   - per-head root-mean-square norm of q and of k with a weight shared by the heads
-//     (v / sqrt(mean(v^2) + eps) * w, 32-bit),
+//     (v / sqrt(mean(v^2) + eps) * w, 32-bit), or the same norm over the whole projection
+//     (all heads of q, or of k, as one vector, with a weight per column),
 //   - rotation of the first rot_dims dimensions of each q and k head by the token's position
 //     (pairs (2i, 2i+1) or (i, i + rot_dims/2); the other dimensions pass),
 //   - a factor on k,
@@ -24,7 +25,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 qkv_prepare_kernel(const void* __restrict__ src, int S, size_t slice, int width, int q_off, int k_off, int v_off,
                    T* __restrict__ q_out, GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
                    int rot_dims, int pairing, const void* q_norm, const void* k_norm, int w_dt, float eps, float k_scale,
-                   int H, int G, int dk, int dv, int dmax, int append, int* status) {
+                   int H, int G, int dk, int dv, int dmax, int append, int norm_whole, int* status) {
     extern __shared__ float heads[];
     gfb_pdl_launch();
     gfb_pdl_wait();
@@ -70,7 +71,26 @@ qkv_prepare_kernel(const void* __restrict__ src, int S, size_t slice, int width,
         ss += x * x;
     }
     const void* nw = is_q ? q_norm : is_k ? k_norm : nullptr;
-    if (nw != nullptr) {
+    if (nw != nullptr && norm_whole) {
+        // the statistic spans every head of the projection; each head's warp adds it up for itself, in the same order
+        const int heads = is_q ? H : G, local = is_q ? head : head - H;
+        const size_t p0 = (size_t)t * width + (is_q ? q_off : k_off);
+        float tot = 0.f;
+        for (int i = lane; i < heads * dk; i += 32) {
+            float x;
+            if (S > 0) {
+                const float* p = (const float*)src;
+                x = 0.f;
+                for (int k = 0; k < S; k++) x += p[(size_t)k * slice + p0 + i];
+            } else {
+                x = gfb_to_f32(((const T*)src)[p0 + i]);
+            }
+            tot += x * x;
+        }
+        tot = gfb_warp_sum(tot);
+        const float r = 1.0f / sqrtf(tot / (float)(heads * dk) + eps);
+        for (int i = lane; i < d; i += 32) v[i] = v[i] * r * ld_w(nw, w_dt, local * dk + i);
+    } else if (nw != nullptr) {
         ss = gfb_warp_sum(ss);
         const float r = 1.0f / sqrtf(ss / (float)d + eps);
         for (int i = lane; i < d; i += 32) v[i] = v[i] * r * ld_w(nw, w_dt, i);
@@ -94,13 +114,13 @@ qkv_prepare_kernel(const void* __restrict__ src, int S, size_t slice, int width,
 
 // src: [T, width] of type dt, or with n_partials > 0 float32 [n_partials][T][width]; q at q_off (H heads of dk), k at
 // k_off (G heads of dk), v at v_off (G heads of dv).  table (or null: no rotation): float32 [table_len][rot_dims/2][2].
-// q_norm / k_norm (or null): [dk] of type w_dt.  append = 0: only q is produced.
+// q_norm / k_norm (or null): [dk] of type w_dt, or with norm_whole [H * dk] and [G * dk].  append = 0: only q is produced.
 GFB_API int gfb_qkv_prepare(const void* src, int n_partials, int width, int q_off, int k_off, int v_off, void* q_out, int dt,
                             void* k_pool, void* v_pool, const int* page_table, int max_pages, int page_size, int n_pages,
                             const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths, int n_seqs,
                             int n_tokens, const float* table, int table_len, int rot_dims, int pairing,
                             const void* q_norm, const void* k_norm, int w_dt, float eps, float k_scale,
-                            int H, int G, int dk, int dv, int append, int* status, cudaStream_t stream) {
+                            int H, int G, int dk, int dv, int append, int norm_whole, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (table != nullptr && (rot_dims % 2 || rot_dims > dk || rot_dims < 0))
         return gfb_fail("gfb_qkv_prepare: %d rotated dimensions in a head of %d", rot_dims, dk);
@@ -116,7 +136,7 @@ GFB_API int gfb_qkv_prepare(const void* src, int n_partials, int width, int q_of
     cudaError_t e;
 #define GO(T) e = gfb_launch(qkv_prepare_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, src, n_partials, slice, \
                              width, q_off, k_off, v_off, (T*)q_out, kv, b, table, table_len, rot_dims, pairing, q_norm, k_norm, \
-                             w_dt, eps, k_scale, H, G, dk, dv, dmax, append, status)
+                             w_dt, eps, k_scale, H, G, dk, dv, dmax, append, norm_whole, status)
     if (dt == GFB_BF16) GO(__nv_bfloat16);
     else if (dt == GFB_F32) GO(float);
     else return gfb_fail("gfb_qkv_prepare: unknown type %d", dt);

@@ -272,7 +272,7 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
 // (q also times q_scale), the decay inputs become the decays g = exp(-exp(A_log_h) softplus(a + dt_bias)).
 __global__ void delta_prepare_kernel(float* __restrict__ qkv, int ldq, int q_off, int k_off, float* __restrict__ a_raw, int ld_a,
                                      int a_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log, int w_dt, int H,
-                                     int KH, int d, float q_scale, float unit_eps) {
+                                     int KH, int d, float q_scale, float unit_eps, int head_decay) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -285,6 +285,11 @@ __global__ void delta_prepare_kernel(float* __restrict__ qkv, int ldq, int q_off
         for (int c = lane; c < d; c += 32) vec[c] *= f;
     }
     float* ar = a_raw + (size_t)t * ld_a + a_off;
+    if (head_decay) {                                          // one decay per head: H numbers per token
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            ar[h] = expf(-expf(ldw(a_log, w_dt, h)) * softplus_f(ar[h] + ldw(dt_bias, w_dt, h)));
+        return;
+    }
     for (int h = 0; h < H; h++) {
         const float rate = expf(ldw(a_log, w_dt, h));
         for (int c = threadIdx.x; c < d; c += blockDim.x)
@@ -294,12 +299,12 @@ __global__ void delta_prepare_kernel(float* __restrict__ qkv, int ldq, int q_off
 
 // qkv [T, ldq] float32 (convolved, activated, q and k unit vectors): query head j at q_off + j * d, key head j at
 // k_off + j * d, value head h at v_off + h * dv.  beta_raw [T, ld_b] of type TD, head h at column beta_off + h.
-// decay [T, ld_a] float32, head h's d channels at a_off + h * d.
+// decay [T, ld_a] float32, head h's d channels at a_off + h * d; with head_decay one number per head, at a_off + h.
 template <typename TD, int RPT>
 __global__ void __launch_bounds__(32 * SCAN_WARPS)
 delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, int v_off, const TD* __restrict__ beta_raw, int ld_b,
                   int beta_off, const float* __restrict__ decay, int ld_a, int a_off, float* __restrict__ state, size_t state_ld,
-                  float* __restrict__ out, GfbBatch b, int H, int KH, int d, int dv, int RG) {
+                  float* __restrict__ out, GfbBatch b, int H, int KH, int d, int dv, int RG, int head_decay) {
     extern __shared__ __align__(16) float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
@@ -330,27 +335,31 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
     }
     __syncthreads();
     float beta_next = 0.f;
-    const bool wide = d % 4 == 0 && ldq % 4 == 0 && ld_a % 4 == 0 && aligned16(qkv + q_off + kh * d) && aligned16(qkv + k_off + kh * d) &&
-                      aligned16(decay + a_off + (size_t)h * d);
+    const bool wide = d % 4 == 0 && ldq % 4 == 0 && aligned16(qkv + q_off + kh * d) && aligned16(qkv + k_off + kh * d) &&
+                      (head_decay || (ld_a % 4 == 0 && aligned16(decay + a_off + (size_t)h * d)));
     auto fetch = [&](int stage, int tile) {
         float* base = sm + stage * STAGE;
         const int nt = min(TB, t1 - tile);
         for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
             const float* row = qkv + (size_t)(tile + tt) * ldq;
-            const float* grow = decay + (size_t)(tile + tt) * ld_a + a_off + (size_t)h * d;
+            const float* grow = decay + (size_t)(tile + tt) * ld_a + a_off + (head_decay ? (size_t)h : (size_t)h * d);
+            if (head_decay) {                                      // the head's one decay stands in every row's place
+                const float g = grow[0];
+                for (int c = lane; c < d; c += 32) base[2 * TB * NP + tt * NP + padded(c, RPT)] = g;
+            }
             if (wide) {                                            // four numbers per copy (a group of RPT rows is contiguous)
                 for (int c = 4 * lane; c < d; c += 128) {
                     const int at = tt * NP + padded(c, RPT);
                     copy_async16(base + at, row + q_off + kh * d + c);
                     copy_async16(base + TB * NP + at, row + k_off + kh * d + c);
-                    copy_async16(base + 2 * TB * NP + at, grow + c);
+                    if (!head_decay) copy_async16(base + 2 * TB * NP + at, grow + c);
                 }
             } else {
                 for (int c = lane; c < d; c += 32) {
                     const int at = tt * NP + padded(c, RPT);
                     copy_async4(base + at, row + q_off + kh * d + c);
                     copy_async4(base + TB * NP + at, row + k_off + kh * d + c);
-                    copy_async4(base + 2 * TB * NP + at, grow + c);
+                    if (!head_decay) copy_async4(base + 2 * TB * NP + at, grow + c);
                 }
             }
             for (int c = lane; c < CB && p0 + c < dv; c += 32) copy_async4(base + 3 * TB * NP + tt * CB + c, row + v_off + (size_t)h * dv + p0 + c);
@@ -472,12 +481,13 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
 }
 
 // state float32: slot stride state_ld, per slot [H][d][dv]; out float32 [T, H, dv]; dt_bias [H * d], a_log [H] of w_dt.
+// head_decay: one decay per head and token instead of one per key channel: a_raw has H columns from a_off, dt_bias is [H].
 // qkv and a_raw are scratch of the caller: q and k are overwritten by their unit vectors, the decay inputs by the decays.
 GFB_API int gfb_delta_rule(float* qkv, int ldq, int q_off, int k_off, int v_off, const void* beta_raw, int b_dt, int ld_b,
                            int beta_off, float* a_raw, int ld_a, int a_off, const void* dt_bias, const void* a_log, int w_dt,
                            float* state, long state_ld, float* out, const int* cu_seqlens, const int* tok_seq, const int* slots,
                            const int* lengths, int n_seqs, int n_tokens, int H, int KH, int d, int dv, float q_scale,
-                           float unit_eps, cudaStream_t stream) {
+                           float unit_eps, int head_decay, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (KH <= 0 || H % KH) return gfb_fail("gfb_delta_rule: %d heads do not divide into %d query/key heads", H, KH);
     int RG = 0;
@@ -489,14 +499,14 @@ GFB_API int gfb_delta_rule(float* qkv, int ldq, int q_off, int k_off, int v_off,
     const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + ROW_PAD) + CB + 1) + (size_t)TB * CB * RG) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = gfb_launch(delta_prepare_kernel, dim3(n_tokens), dim3(128), 0, stream, qkv, ldq, q_off, k_off, a_raw, ld_a, a_off,
-                               dt_bias, a_log, w_dt, H, KH, d, q_scale, unit_eps);
+                               dt_bias, a_log, w_dt, H, KH, d, q_scale, unit_eps, head_decay);
     if (gfb_check(e, "gfb_delta_rule (prepare)")) return 1;
 #define GO(TD, R)                                                                                                          \
     do {                                                                                                                   \
         if (allow_smem(delta_rule_kernel<TD, R>, smem, "gfb_delta_rule")) return 1;                                        \
         e = gfb_launch(delta_rule_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, (const float*)qkv, ldq, \
                        q_off, k_off, v_off, (const TD*)beta_raw, ld_b, beta_off, (const float*)a_raw, ld_a, a_off, state,  \
-                       (size_t)state_ld, out, b, H, KH, d, dv, RG);                                                        \
+                       (size_t)state_ld, out, b, H, KH, d, dv, RG, head_decay);                                            \
     } while (0)
 #define PICK(TD) do { if (rpt == 8) GO(TD, 8); else if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
     if (b_dt == GFB_BF16) PICK(__nv_bfloat16);

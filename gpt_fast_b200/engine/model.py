@@ -12,7 +12,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
-from ..cache import Cache, CacheNeeds
+from ..cache import Cache, CacheNeeds, EntryView
 from ..config.spec import ModelSpec, PartSpec
 from ..ops.types import BatchMeta
 from ..parts.residual import Residual
@@ -60,6 +60,7 @@ class Transformer:
         self.embedding = None if spec.embedding is None else build_part(EMBEDDINGS, spec.embedding, dtype=self.dtype)
         self.embed_weight = None
         self.head_weight = None
+        self.after_layer = None            # a callable(Residual) run behind every layer of a step (tests look at the stream)
 
     # ---- parameters -------------------------------------------------------------
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -198,7 +199,14 @@ class Transformer:
             self.embedding.forward(tokens, self.embed_weight, x, batch, cache.view(EMBEDDING_CACHE_ENTRY), scale)
         x = Residual(x)
         for e in self.spec.schedule:
-            self.blocks[e.layer].forward(x, batch, cache.view(e.cache), append=e.owns_cache)
+            if e.kv_from is None:
+                self.blocks[e.layer].forward(x, batch, cache.view(e.cache), append=e.owns_cache)
+            else:
+                # another entry's keys and values, the run's own state
+                view = EntryView(kv=cache.view(e.kv_from).kv, state=cache.view(e.cache).state)
+                self.blocks[e.layer].forward(x, batch, view, append=False)
+            if self.after_layer is not None:
+                self.after_layer(x)
         W = T if want_rows is None else (n_want if n_want is not None else want_rows.shape[0])
         logits = torch.empty(W, self.vocab_size, dtype=torch.float32, device=self.device)
         if W:

@@ -92,6 +92,12 @@ def embed(tokens, table, out, status, scale: float = 1.0):
     return kernels().embed(tokens, table, out, status, scale)
 
 
+def embed_positions(tokens, table, positions, out, batch: BatchMeta, scale: float = 1.0):
+    """out[t] = table[tokens[t]] * scale + positions[p_t], p_t the token's place in its sequence.  positions [P, D] of the
+    table's type; out float32 [T, D]."""
+    return kernels().embed_positions(tokens, table, positions, out, batch, scale)
+
+
 def embed_hashed(tokens, table, extra, out, batch: BatchMeta, prev, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0):
     """out[t] = table[tokens[t]] * scale + extra[(previous token * mul_prev + tokens[t] * mul_cur) mod buckets], with
     extra's row `buckets` for a sequence's first token.  extra [buckets + 1, D]; prev int32 [n_slots] is per-sequence
@@ -172,7 +178,8 @@ def ssd_scan(x, b_off: int, c_off: int, dt_src, dt_off: int, dt_bias, a_log, ski
 
 
 def delta_rule(qkv, offsets, beta_src, beta_off: int, a_src, a_off: int, dt_bias, a_log, state, state_off: int, out,
-               batch: BatchMeta, n_head: int, n_qk: int, head_dim: int, v_head_dim: int, q_scale: float, unit_eps: float = 1e-6):
+               batch: BatchMeta, n_head: int, n_qk: int, head_dim: int, v_head_dim: int, q_scale: float, unit_eps: float = 1e-6,
+               head_decay: bool = False):
     """Gated delta rule, token after token: per head h (query/key head j = h // (n_head / n_qk)), with q and k divided
     by sqrt(sum of squares + unit_eps) (q also times q_scale), beta = sigmoid(beta_src[:, beta_off + h]) and
     g = exp(-exp(a_log[h]) softplus(a_src[:, a_off + h * head_dim + i] + dt_bias[h * head_dim + i])):
@@ -180,9 +187,13 @@ def delta_rule(qkv, offsets, beta_src, beta_off: int, a_src, a_off: int, dt_bias
     qkv float32 [T, W] with q, k, v at the column offsets `offsets`; a_src float32; state float32 [n_slots, S] holds
     [n_head, head_dim, v_head_dim] per sequence from column state_off; out float32 [T, n_head, v_head_dim].
     qkv and a_src are the caller's scratch: the kernels overwrite q and k by their unit vectors and the decay inputs by the
-    decays."""
+    decays.  head_decay: one decay per head and token, g = exp(-exp(a_log[h]) softplus(a_src[:, a_off + h] + dt_bias[h])),
+    dt_bias being [n_head]."""
+    if not head_decay:
+        return kernels().delta_rule(qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch,
+                                    n_head, n_qk, head_dim, v_head_dim, q_scale, unit_eps)
     return kernels().delta_rule(qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch,
-                                n_head, n_qk, head_dim, v_head_dim, q_scale, unit_eps)
+                                n_head, n_qk, head_dim, v_head_dim, q_scale, unit_eps, head_decay=True)
 
 
 def gated_norm(y, gate, gate_off: int, weight, out, group: int, eps: float, act: str = "silu", gate_first: bool = False):
@@ -194,15 +205,19 @@ def gated_norm(y, gate, gate_off: int, weight, out, group: int, eps: float, act:
 
 def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, n_kv: int, head_dim: int,
                 v_head_dim: int, table=None, rot_dims: int = 0, pairing: str = "half", q_norm=None, k_norm=None,
-                norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True):
+                norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True, norm_whole: bool = False):
     """From a projection's row to attention's inputs.  src [T, W] holds q (H heads of head_dim), k (G heads of
     head_dim) and v (G heads of v_head_dim) at the column offsets `offsets` = (q, k, v); with `partials` (float32
     [S, T, W]) src is their sum.  Per head, in this order: root-mean-square norm of q and k with the weights
     q_norm / k_norm [head_dim] (None: none), rotation of the first rot_dims dimensions by the token's position from
     `table` (None: none), k times k_scale.  q goes to q_out [T, H, head_dim], k and v to the token's place in the
-    cache (unless append is False)."""
+    cache (unless append is False).  norm_whole: the norm's mean square runs over all heads of q (of k) at once and the
+    weights are [H * head_dim] and [G * head_dim]."""
+    if not norm_whole:
+        return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
+                                     rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append)
     return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
-                                 rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append)
+                                 rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append, norm_whole=True)
 
 
 def retention(src, offsets, state, out, batch: BatchMeta, n_head: int, head_dim: int, v_head_dim: int, decay, table=None,
@@ -218,6 +233,26 @@ def retention_gate(o, src, gate_offset: int, out, n_head: int, v_head_dim: int, 
     """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]) with the gate at column
     gate_offset of src [T, W]; o float32 [T, H, dv]; out [T, H*dv] in the compute type."""
     return kernels().retention_gate(o, src, gate_offset, out, n_head, v_head_dim, eps)
+
+
+def sigmoid_gate(y, gate, gate_off: int, group: int):
+    """y[t, c] *= sigmoid(gate[t, gate_off + c // group]), in place: one gate per `group` columns of y [T, C]; gate
+    [T, Wg] of y's type."""
+    return kernels().sigmoid_gate(y, gate, gate_off, group)
+
+
+def moe_route(logits, correction, top: int, scale: float, idx, weights):
+    """Choice of experts.  logits float32 [T, >= E] (the first E columns count, E = len(correction)): s = sigmoid(logits);
+    the `top` experts with the largest s + correction (lowest index on ties) go to idx int32 [T, top], and
+    weights float32 [T, top] = their s / (sum of the chosen s + 1e-20) * scale."""
+    return kernels().moe_route(logits, correction, top, scale, idx, weights)
+
+
+def moe_experts(h, idx, weights, w13, w2, x, limit: float, alpha: float, shift: float = 1.0):
+    """x float32 [T, D] += sum_r weights[t, r] * W2_e (g * sigmoid(alpha g) * (u + shift)), e = idx[t, r],
+    g = min(gate_e h, limit), u = clamp(up_e h, -limit, limit) (limit <= 0: no clamps).  w13 [E, 2F, D]: rows alternate
+    gate, up; w2 [E, D, F]; h [T, D] of the weights' type."""
+    return kernels().moe_experts(h, idx, weights, w13, w2, x, limit, alpha, shift)
 
 
 def activation(x, kind: str, out=None):
@@ -262,12 +297,17 @@ def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n
 
 def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int] = None, chunk: Optional[int] = None, sink=None, v_head_dim: Optional[int] = None,
-              values_in_keys: bool = False):
+              values_in_keys: bool = False, bias=None, slopes=None):
     """Causal grouped-query attention of q [T, H, d] over the cache (which
     already holds this step's keys and values); out [T, H*dv].  chunk: a query sees only the keys of its own block
     of `chunk` positions (counted from the sequence's first position).  sink (float32 [H]): exp(sink_h) joins the
     softmax denominator of head h, with no value.  v_head_dim: the values' head size if it differs from d.
-    values_in_keys: a key's first v_head_dim numbers are also its value (the value pool is not read)."""
+    values_in_keys: a key's first v_head_dim numbers are also its value (the value pool is not read).
+    bias (float32 [L, H]): bias[min(n, L - 1), h] is added to the scaled score of a key n positions back.
+    slopes (float32 [H]): slopes[h] * n is taken off it."""
+    if bias is not None or slopes is not None:
+        return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
+                                   values_in_keys=values_in_keys, bias=bias, slopes=slopes)
     if values_in_keys:
         return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
                                    values_in_keys=True)

@@ -129,6 +129,17 @@ class CudaKernels:
                    *self._batch_args(batch), _ptr(prev), c_int(D), c_int(V), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
                    c_float(scale), _ptr(batch.status), _stream())
 
+    def embed_positions(self, tokens, table, positions, out, batch, scale=1.0):
+        T = tokens.shape[0]
+        V, D = table.shape
+        _need(tokens, torch.int32, (batch.n_tokens,), "tokens")
+        _need(table, name="embedding table")
+        _need(positions, table.dtype, (positions.shape[0], D), "position table")
+        _need(out, torch.float32, (T, D), "embedding output")
+        self._call("embedding", "gfb_embed_positions", _ptr(tokens), _ptr(table), _ptr(positions), c_int(_dt(table)), _ptr(out),
+                   *self._batch_args(batch), c_int(D), c_int(V), c_int(positions.shape[0]), c_float(scale), _ptr(batch.status),
+                   _stream())
+
     def softcap(self, x, cap):
         _need(x, torch.float32, name="logits")
         self._call("core", "gfb_softcap", _ptr(x), c_long(x.numel()), c_float(cap), _stream())
@@ -363,7 +374,7 @@ class CudaKernels:
                    _ptr(out), *self._batch_args(batch), c_int(n_head), c_int(head_dim), c_int(n_state), c_int(n_groups), _stream())
 
     def delta_rule(self, qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch, n_head,
-                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6):
+                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6, head_decay=False):
         T = batch.n_tokens
         q_off, k_off, v_off = offsets
         _need(qkv, torch.float32, name="q, k, v")
@@ -371,16 +382,18 @@ class CudaKernels:
             _fail(f"q, k and v at {offsets} do not fit rows of {tuple(qkv.shape)}")
         _need(beta_src, name="beta")
         _need(a_src, torch.float32, name="decay input")
-        if beta_src.shape[0] != T or beta_off + n_head > beta_src.shape[1] or a_src.shape[0] != T or a_off + n_head * head_dim > a_src.shape[1]:
+        per_head = 1 if head_decay else head_dim
+        if beta_src.shape[0] != T or beta_off + n_head > beta_src.shape[1] or a_src.shape[0] != T or a_off + n_head * per_head > a_src.shape[1]:
             _fail("beta or the decay input do not fit their rows")
-        _need(dt_bias, shape=(n_head * head_dim,), name="dt_bias")
+        _need(dt_bias, shape=(n_head * per_head,), name="dt_bias")
         _need(a_log, dt_bias.dtype, (n_head,), "A_log")
         _need(out, torch.float32, (T, n_head, v_head_dim), "delta-rule output")
         sp, sld = self._state_args(state, state_off, n_head * head_dim * v_head_dim)
         self._call("recurrent", "gfb_delta_rule", _ptr(qkv), c_int(qkv.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
                    _ptr(beta_src), c_int(_dt(beta_src)), c_int(beta_src.shape[1]), c_int(beta_off), _ptr(a_src), c_int(a_src.shape[1]),
                    c_int(a_off), _ptr(dt_bias), _ptr(a_log), c_int(_dt(dt_bias)), sp, sld, _ptr(out), *self._batch_args(batch),
-                   c_int(n_head), c_int(n_qk), c_int(head_dim), c_int(v_head_dim), c_float(q_scale), c_float(unit_eps), _stream())
+                   c_int(n_head), c_int(n_qk), c_int(head_dim), c_int(v_head_dim), c_float(q_scale), c_float(unit_eps),
+                   c_int(1 if head_decay else 0), _stream())
 
     def gated_norm(self, y, gate, gate_off, weight, out, group, eps, act="silu", gate_first=False):
         T, C = y.shape
@@ -397,7 +410,7 @@ class CudaKernels:
                    c_int(group), c_float(eps), c_int(1 if act == "sigmoid" else 0), c_int(1 if gate_first else 0), _stream())
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
-                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True):
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False):
         T = batch.n_tokens
         if partials is not None:
             W = partials.shape[2]
@@ -408,7 +421,8 @@ class CudaKernels:
             _need(src, q_out.dtype, (T, W), "projection")
             source, n_part = src, 0
         q_off, k_off, v_off = offsets
-        if max(q_off + n_head * head_dim, k_off + n_kv * head_dim, v_off + n_kv * v_head_dim) > W:
+        ends = [q_off + n_head * head_dim] + ([k_off + n_kv * head_dim, v_off + n_kv * v_head_dim] if append else [])
+        if max(ends) > W:
             _fail(f"q, k and v at {offsets} do not fit rows of {W}")
         _need(q_out, shape=(T, n_head, head_dim), name="q_out")
         if table is not None:
@@ -416,9 +430,9 @@ class CudaKernels:
             if table.shape[1] * 2 != rot_dims:
                 _fail(f"the rotary table serves {table.shape[1] * 2} dimensions, the mixer rotates {rot_dims}")
         w_dt = 0
-        for wn in (q_norm, k_norm):
+        for wn, heads in ((q_norm, n_head), (k_norm, n_kv)):
             if wn is not None:
-                _need(wn, shape=(head_dim,), name="q/k norm weight")
+                _need(wn, shape=((heads if norm_whole else 1) * head_dim,), name="q/k norm weight")
                 w_dt = _dt(wn)
         if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
             _fail("the q and k norm weights must have one type")
@@ -431,8 +445,8 @@ class CudaKernels:
                    _ptr(q_out), c_int(_dt(q_out)), *self._kv_args(kv), *self._batch_args(batch), _ptr(table),
                    c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
                    c_int(_PAIRING[pairing]), _ptr(q_norm), _ptr(k_norm), c_int(w_dt), c_float(norm_eps), c_float(k_scale),
-                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(v_head_dim), c_int(1 if append else 0), _ptr(batch.status),
-                   _stream())
+                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(v_head_dim), c_int(1 if append else 0),
+                   c_int(1 if norm_whole else 0), _ptr(batch.status), _stream())
 
     def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
                   pairing="half", k_scale=1.0):
@@ -470,6 +484,65 @@ class CudaKernels:
             _fail(f"a gate at column {gate_offset} does not fit rows of {W}")
         self._call("retention", "gfb_retention_gate", _ptr(o), _ptr(src), c_int(_dt(src)), c_int(W), c_int(gate_offset), _ptr(out),
                    c_int(T), c_int(n_head), c_int(v_head_dim), c_float(eps), _stream())
+
+    def sigmoid_gate(self, y, gate, gate_off, group):
+        T, C = y.shape
+        _need(y, name="gated tensor")
+        _need(gate, y.dtype, name="gate")
+        if gate.dim() != 2 or gate.shape[0] != T or group < 1 or C % group or gate_off + C // group > gate.shape[1]:
+            _fail(f"gates for groups of {group} of {C} columns at column {gate_off} do not fit {tuple(gate.shape)}")
+        self._call("elementwise", "gfb_sigmoid_gate", _ptr(y), _ptr(gate), c_int(_dt(y)), c_int(T), c_int(C), c_int(gate.shape[1]),
+                   c_int(gate_off), c_int(group), _stream())
+
+    # -- mixture of experts ------------------------------------------------------------------
+    MOE_TILE_ROWS = 64                 # rows of a tile of the sorted form
+    MOE_FEW_TOKENS = 32                # up to this many tokens a warp per output number streams the weight rows
+
+    def moe_route(self, logits, correction, top, scale, idx, weights):
+        T = logits.shape[0]
+        E = correction.shape[0]
+        _need(logits, torch.float32, name="router logits")
+        if logits.dim() != 2 or logits.shape[1] < E:
+            _fail(f"router logits {tuple(logits.shape)} for {E} experts")
+        _need(correction, name="router correction")
+        _need(idx, torch.int32, (T, top), "chosen experts")
+        _need(weights, torch.float32, (T, top), "expert weights")
+        self._call("moe", "gfb_moe_route", _ptr(logits), c_int(logits.shape[1]), _ptr(correction), c_int(_dt(correction)), c_int(E),
+                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), _stream())
+
+    def moe_experts(self, h, idx, weights, w13, w2, x, limit, alpha, shift=1.0):
+        T, D = h.shape
+        E, F2, _ = w13.shape
+        F, top = F2 // 2, idx.shape[1]
+        _need(h, name="expert input")
+        _need(w13, h.dtype, (E, 2 * F, D), "gate/up weights")
+        _need(w2, h.dtype, (E, D, F), "down weights")
+        _need(idx, torch.int32, (T, top), "chosen experts")
+        _need(weights, torch.float32, (T, top), "expert weights")
+        _need(x, torch.float32, (T, D), "residual stream")
+        dt = c_int(_dt(h))
+        sizes = (c_int(T), c_int(top), c_int(E), c_int(F), c_int(D))
+        if T <= self.MOE_FEW_TOKENS:
+            act = torch.empty(T * top, F, dtype=h.dtype, device=h.device)
+            self._call("moe", "gfb_moe_glu", _ptr(h), _ptr(idx), _ptr(w13), _ptr(act), dt, *sizes, c_float(limit), c_float(alpha),
+                       c_float(shift), _ptr(None), _ptr(None), c_int(0), _stream())
+            self._call("moe", "gfb_moe_down", _ptr(act), _ptr(idx), _ptr(weights), _ptr(w2), _ptr(x), dt, *sizes, _ptr(None), _ptr(None),
+                       c_int(0), _ptr(None), _stream())
+            return
+        # the sorted form: pairs grouped by expert, every expert's rows padded to whole tiles
+        rows = self.MOE_TILE_ROWS
+        pairs = T * top
+        tiles = (pairs + min(E, pairs) * (rows - 1)) // rows
+        plan = torch.empty(tiles * rows + pairs + tiles, dtype=torch.int32, device=h.device)
+        row_pair, pair_row, tile_expert = plan[:tiles * rows], plan[tiles * rows:tiles * rows + pairs], plan[tiles * rows + pairs:]
+        self._call("moe", "gfb_moe_plan", _ptr(idx), c_int(pairs), c_int(E), c_int(rows), _ptr(row_pair), _ptr(pair_row),
+                   _ptr(tile_expert), c_int(tiles), _stream())
+        act = torch.empty(tiles * rows, F, dtype=h.dtype, device=h.device)
+        y = torch.empty(pairs, D, dtype=torch.float32, device=h.device)
+        self._call("moe", "gfb_moe_glu", _ptr(h), _ptr(idx), _ptr(w13), _ptr(act), dt, *sizes, c_float(limit), c_float(alpha),
+                   c_float(shift), _ptr(row_pair), _ptr(tile_expert), c_int(tiles), _stream())
+        self._call("moe", "gfb_moe_down", _ptr(act), _ptr(idx), _ptr(weights), _ptr(w2), _ptr(x), dt, *sizes, _ptr(row_pair),
+                   _ptr(tile_expert), c_int(tiles), _ptr(y), _stream())
 
     def activation(self, x, kind, out=None):
         if kind not in _UNARY:
@@ -566,7 +639,7 @@ class CudaKernels:
 
     # -- attention ---------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
-                  values_in_keys=False):
+                  values_in_keys=False, bias=None, slopes=None):
         T = batch.n_tokens
         dv = v_head_dim or head_dim
         _need(q, shape=(T, n_head, head_dim), name="q")
@@ -574,8 +647,13 @@ class CudaKernels:
         _need(kv.k_pool, q.dtype, name="key pool")
         if sink is not None:
             _need(sink, torch.float32, (n_head,), "sink")
-        plain = chunk is None and sink is None
-        if (values_in_keys and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
+        if bias is not None:
+            _need(bias, torch.float32, (bias.shape[0], n_head), "distance bias table")
+        if slopes is not None:
+            _need(slopes, torch.float32, (n_head,), "distance slopes")
+        biased = bias is not None or slopes is not None
+        plain = chunk is None and sink is None and not biased
+        if (values_in_keys and not biased and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
                 and not window and head_dim % 16 == 0 and dv % 16 == 0 and dv <= 512 and dv < head_dim and kv.page_size % 32 == 0
                 and (64 + 2 * 32) * (head_dim + 8) * 2 <= 220 * 1024):
             # a latent that all heads share: the tensor-core kernel that fetches every cached row once per 64 (token, head)
@@ -592,14 +670,14 @@ class CudaKernels:
                               c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
                               c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), c_int(splits),
                               _ptr(scratch), _ptr(batch.status), _stream())
-        if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+        if (not values_in_keys and not biased and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
                 and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
             # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for
             return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
                    c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), c_int(1 if values_in_keys else 0),
-                   _ptr(batch.status), _stream())
+                   _ptr(bias), c_int(bias.shape[0] if bias is not None else 0), _ptr(slopes), _ptr(batch.status), _stream())
 
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)

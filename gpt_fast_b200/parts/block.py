@@ -112,13 +112,16 @@ class ParallelBlock:
     s1, s2: learned per-column factors (`layer_scale`; without it they are 1).  The feed-forward with its norm is
     optional.  The two norms share mean and variance and differ in their weights, so one kernel writes both normed
     rows; the two scaled sums are left to the stream and done by the next layer's norm kernel on its way
-    (`Residual.add_scaled`).  The norms are layer norms without bias."""
+    (`Residual.add_scaled`).  The norms are layer norms without bias.
+
+    A feed-forward WITHOUT a norm of its own reads the mixer's norm: x += mixer(h) + feed_forward(h), h = norm1(x); the
+    norm may then be of any kind.  Without layer scale both sublayers add straight into the stream."""
     roles = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "ffn_norm": "norm"}
     optional_roles = ("feed_forward", "ffn_norm")
 
     def __init__(self, parts: dict, dim: int, dtype: torch.dtype, layer_scale: bool = False):
-        if ("feed_forward" in parts) != ("ffn_norm" in parts):
-            raise ValueError("a parallel block has a feed-forward together with its norm, or neither")
+        if "ffn_norm" in parts and "feed_forward" not in parts:
+            raise ValueError("a parallel block has no norm for a feed-forward it lacks")
         self._parts = dict(parts)
         self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
         self.feed_forward, self.ffn_norm = parts.get("feed_forward"), parts.get("ffn_norm")
@@ -139,7 +142,15 @@ class ParallelBlock:
         x = as_residual(x)
         T, dev = x.x.shape[0], x.x.device
         h1 = torch.empty(T, self.dim, dtype=self.dtype, device=dev)
-        if self.feed_forward is not None:
+        if self.ffn_norm is None:                              # one norm, read by both sublayers
+            self.mixer_norm.forward(x, h1)
+            if self.mixer_scale is None:
+                self.mixer.forward(h1, batch, view, residual=x, append=append)
+                if self.feed_forward is not None:
+                    self.feed_forward.forward(h1, residual=x)
+                return
+            h2 = h1
+        elif self.feed_forward is not None:
             h2 = torch.empty(T, self.dim, dtype=self.dtype, device=dev)
             self.mixer_norm.forward_with(self.ffn_norm, x, h1, h2)
         else:

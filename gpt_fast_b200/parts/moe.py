@@ -1,0 +1,67 @@
+"""Mixture of experts as a feed-forward: every token runs `top` of `n_experts` small gated feed-forwards.
+
+    z = W_router h                      router logits, 32-bit
+    s = sigmoid(z);  chosen = the `top` experts with the largest s + correction  (the correction counts for the choice only)
+    w_e = s_e / (sum of the chosen s + 1e-20) * scale
+    expert e:  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit),  y = W_down (g * sigmoid(alpha g) * (u + shift))
+    result = sum over the chosen e of w_e * y_e
+
+The experts have no biases.  Their gate and up rows alternate in one matrix per expert, so one product yields both and
+applies the activation before anything is written; the weighted sum of the chosen experts' outputs is added to the
+residual stream in 32-bit by the kernel that does the down products (or by the one behind it)."""
+import torch
+
+from .. import ops
+from ..weights.loader import ParamSpec
+from . import register_feed_forward
+from .residual import as_residual
+
+
+def _pad_rows(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:
+    extra = -w.shape[0] % multiple
+    return w.contiguous() if extra == 0 else torch.cat([w, w.new_zeros(extra, w.shape[1])]).contiguous()
+
+
+@register_feed_forward("moe")
+class MixtureOfExperts:
+    def __init__(self, dim: int, hidden: int, n_experts: int, top: int, dtype: torch.dtype, router_scale: float = 1.0,
+                 limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0, correction: bool = True):
+        if not 1 <= top <= n_experts:
+            raise ValueError(f"{top} of {n_experts} experts per token")
+        self.dim, self.hidden, self.n_experts, self.top, self.dtype = dim, hidden, int(n_experts), int(top), dtype
+        self.router_scale, self.limit, self.alpha, self.shift = float(router_scale), float(limit), float(alpha), float(shift)
+        self.has_correction = bool(correction)
+        self.router = self.correction = self.w13 = self.w2 = None
+
+    def param_specs(self):
+        E, F, D = self.n_experts, self.hidden, self.dim
+        specs = {"router": ParamSpec((E, D)), "gate": ParamSpec((E, F, D)), "up": ParamSpec((E, F, D)), "down": ParamSpec((E, D, F))}
+        if self.has_correction:
+            specs["correction"] = ParamSpec((E,), "vector")
+        return specs
+
+    def load(self, tensors):
+        E, F, D = self.n_experts, self.hidden, self.dim
+        self._router_stored = tensors["router"]
+        self.router = _pad_rows(tensors["router"])
+        self.correction = tensors["correction"] if self.has_correction else torch.zeros(E, dtype=torch.float32, device=tensors["router"].device)
+        # rows alternate gate, up within every expert
+        self.w13 = torch.stack([tensors["gate"], tensors["up"]], dim=2).reshape(E, 2 * F, D).contiguous()
+        self.w2 = tensors["down"]
+
+    def export(self):
+        w = self.w13.view(self.n_experts, self.hidden, 2, self.dim)
+        out = {"router": self._router_stored, "gate": w[:, :, 0], "up": w[:, :, 1], "down": self.w2}
+        if self.has_correction:
+            out["correction"] = self.correction
+        return out
+
+    def forward(self, h, residual):
+        T = h.shape[0]
+        z = torch.empty(T, self.router.shape[0], dtype=torch.float32, device=h.device)
+        ops.linear(h, self.router, z)
+        idx = torch.empty(T, self.top, dtype=torch.int32, device=h.device)
+        w = torch.empty(T, self.top, dtype=torch.float32, device=h.device)
+        ops.moe_route(z, self.correction, self.top, self.router_scale, idx, w)
+        x = as_residual(residual).tensor()                     # complete: the experts' kernel adds into it
+        ops.moe_experts(h, idx, w, self.w13, self.w2, x, self.limit, self.alpha, self.shift)

@@ -69,6 +69,42 @@ class PlainOps:
         out.copy_(table[ids.clamp(0, table.shape[0] - 1)].float() * scale)
         out[bad] = 0
 
+    def embed_positions(self, tokens, table, positions, out, batch, scale=1.0):
+        pos, _ = token_positions(batch)
+        if int(pos.max()) >= positions.shape[0]:
+            raise IndexError("position beyond the position table")
+        out.copy_((table[tokens.long()].double() * scale + positions[pos].double()).float())
+
+    def sigmoid_gate(self, y, gate, gate_off, group):
+        C = y.shape[1]
+        g = torch.sigmoid(gate[:, gate_off:gate_off + C // group].double()).repeat_interleave(group, dim=1)
+        y.copy_((y.double() * g).to(y.dtype))
+
+    # -- mixture of experts ---------------------------------------------------------------------
+    def moe_route(self, logits, correction, top, scale, idx, weights):
+        E = correction.shape[0]
+        s = torch.sigmoid(logits[:, :E].float())
+        choice = s + correction.float()
+        for t in range(s.shape[0]):
+            order = sorted(range(E), key=lambda e: (-float(choice[t, e]), e))[:top]
+            picked = s[t, order]
+            idx[t] = torch.tensor(order, dtype=idx.dtype)
+            weights[t] = picked / (picked.sum() + 1e-20) * scale
+
+    def moe_experts(self, h, idx, weights, w13, w2, x, limit, alpha, shift=1.0):
+        hd = h.double()
+        for t in range(h.shape[0]):
+            acc = torch.zeros(x.shape[1], dtype=torch.float64)
+            for r in range(idx.shape[1]):
+                e = int(idx[t, r])
+                z = w13[e].double() @ hd[t]
+                g, u = z[0::2], z[1::2]
+                if limit > 0:
+                    g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+                a = (g * torch.sigmoid(alpha * g) * (u + shift)).to(h.dtype).double()
+                acc += float(weights[t, r]) * (w2[e].double() @ a)
+            x[t] = (x[t].double() + acc).float()
+
     def rmsnorm(self, x, weight, eps, out, rows=None, pending=None):
         if pending is not None:
             self.add_partials(x, pending)
@@ -182,7 +218,7 @@ class PlainOps:
             out[t] = y.float()
 
     def delta_rule(self, qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch, n_head,
-                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6):
+                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6, head_decay=False):
         H, J, d, dv = n_head, n_qk, head_dim, v_head_dim
         T = batch.n_tokens
         x = qkv.double()
@@ -193,8 +229,11 @@ class PlainOps:
         q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale).repeat_interleave(H // J, dim=1)
         k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(H // J, dim=1)
         beta = torch.sigmoid(beta_src[:, beta_off:beta_off + H].double())
-        a = a_src[:, a_off:a_off + H * d].double() + dt_bias.double()
-        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * torch.nn.functional.softplus(a).view(T, H, d))
+        if head_decay:
+            a = (a_src[:, a_off:a_off + H].double() + dt_bias.double())[:, :, None].expand(T, H, d)
+        else:
+            a = (a_src[:, a_off:a_off + H * d].double() + dt_bias.double()).view(T, H, d)
+        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * torch.nn.functional.softplus(a))
         _, slots = token_positions(batch)
         for t in range(T):
             slot = int(slots[t])
@@ -228,15 +267,24 @@ class PlainOps:
         return out
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
-                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True):
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False):
         H, G, d, dv = n_head, n_kv, head_dim, v_head_dim
         T = batch.n_tokens
         x = (partials.double().sum(0) if partials is not None else src.double())
         qo, ko, vo = offsets
         q = x[:, qo:qo + H * d].reshape(T, H, d)
-        k = x[:, ko:ko + G * d].reshape(T, G, d)
-        v = x[:, vo:vo + G * dv].reshape(T, G, dv)
+        if append:
+            k = x[:, ko:ko + G * d].reshape(T, G, d)
+            v = x[:, vo:vo + G * dv].reshape(T, G, dv)
+        else:                                                  # only q is made: the row may hold no keys or values at all
+            k, k_norm = x.new_zeros(T, G, d), None
         pos, slots = token_positions(batch)
+        if norm_whole:
+            if q_norm is not None:
+                q = q * torch.rsqrt((q * q).mean((-2, -1), keepdim=True) + norm_eps) * q_norm.double().view(H, d)
+            if k_norm is not None:
+                k = k * torch.rsqrt((k * k).mean((-2, -1), keepdim=True) + norm_eps) * k_norm.double().view(G, d)
+            q_norm = k_norm = None
         if q_norm is not None:
             q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps) * q_norm.double()
         if k_norm is not None:
@@ -362,7 +410,7 @@ class PlainOps:
 
     # -- attention -----------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
-                  values_in_keys=False):
+                  values_in_keys=False, bias=None, slopes=None):
         H, G, d = n_head, n_kv, head_dim
         dv = v_head_dim or head_dim
         pos, slots = token_positions(batch)
@@ -382,6 +430,10 @@ class PlainOps:
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
             s = torch.einsum("hd,nhd->hn", q[t].double(), k) * scale
+            if bias is not None:
+                s = s + bias.double()[(p - j).clamp(max=bias.shape[0] - 1)].T
+            if slopes is not None:
+                s = s - slopes.double()[:, None] * (p - j).double()[None, :]
             if sink is not None:
                 w = torch.softmax(torch.cat([s, sink.double()[:, None]], dim=-1), -1)[:, :-1]
             else:
