@@ -185,7 +185,7 @@ class PlainOps:
         cu = batch.cu_seqlens.tolist()
         for s in range(batch.n_seqs):
             slot = int(batch.slots[s])
-            old = state[slot, state_off:state_off + (taps - 1) * C].double().view(taps - 1, C)
+            old = state[slot, state_off:state_off + (taps - 1) * C].double().view(taps - 1, C) if taps > 1 else x.new_zeros(0, C)
             seq = torch.cat([old, x[cu[s]:cu[s + 1]]])
             n = cu[s + 1] - cu[s]
             y = torch.zeros(n, C, dtype=torch.float64)
@@ -194,7 +194,8 @@ class PlainOps:
             if bias is not None:
                 y += bias.double()
             out[cu[s]:cu[s + 1]] = (y / (1 + torch.exp(-y)) if act else y).float()
-            state[slot, state_off:state_off + (taps - 1) * C] = seq[n:].reshape(-1).float()
+            if taps > 1:                                           # one tap carries nothing
+                state[slot, state_off:state_off + (taps - 1) * C] = seq[n:].reshape(-1).float()
 
     def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
                  n_state, n_groups):

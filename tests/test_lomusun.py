@@ -1,0 +1,357 @@
+"""The Lomusun decoder through the whole engine, against the plain statement in `plain_lomusun.py`: two small
+configurations that differ in every size and option (grouped and ungrouped heads, one head, value heads larger and smaller
+than key heads, convolutions of 1 to 5 taps, windows of 1 position and windows longer than any prompt, distance tables with
+an even and an odd number of rows and a fractional far distance, readers of another layer's keys and values with other
+windows and other query heads than the owner, 1 of 40 and 3 of 3 experts, layers without a feed-forward, both orders of the
+two kinds of layer), random weights.
+
+Every test runs three ways: the host logic on the CPU against the plain statement of the kernels, and the kernels
+themselves in 32-bit and in bfloat16 on a GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+from safetensors.torch import load_file
+
+import gpt_fast_b200 as gf
+from gpt_fast_b200 import ops
+from gpt_fast_b200.engine.step import Stepper
+import plain_lomusun as pl
+import plain_ops
+import traces
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+NAMES = ["lomusun-tiny-a", "lomusun-tiny-b"]
+BACKENDS = [
+    pytest.param(("cpu", "float32"), id="cpu-standin-f32"),
+    pytest.param(("cuda", "float32"), id="cuda-f32", marks=pytest.mark.gpu),
+    pytest.param(("cuda", "bfloat16"), id="cuda-bf16", marks=pytest.mark.gpu),
+]
+
+
+@pytest.fixture(params=BACKENDS)
+def backend(request):
+    device, dtype = request.param
+    prev = ops.use_kernels(plain_ops.PlainOps()) if device == "cpu" else None
+    yield device, dtype
+    if device == "cpu":
+        ops.use_kernels(prev)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for i, name in enumerate(NAMES):
+        d = str(tmp_path_factory.mktemp(name.replace("-", "_")))
+        gf.write_model_folder(d, name, seed=61 + i, std=0.11, jitter=0.2, vector_dtype="float32" if i else "bfloat16")
+        out[name] = d
+    return out
+
+
+_plain_cache = {}
+
+
+def plain(folder, tokens):
+    key = (folder, tuple(tokens))
+    if key not in _plain_cache:
+        with open(os.path.join(folder, "config.json")) as f:
+            cfg = json.load(f)
+        _plain_cache[key] = pl.forward(cfg, load_file(os.path.join(folder, "model.safetensors")), tokens).float()
+    return _plain_cache[key]
+
+
+def judge(got, folder, tokens, rows, dtype, where):
+    """32-bit: equal to rounding.  bfloat16: the error over all rows within a few per cent of the logits' own scale, and all
+    rows but a few within a tenth of it (a bfloat16 input may tip a close call of the router at a token or two, which moves
+    that token's logits by a fraction of their scale; a wrong key, page or state moves most rows by about the scale)."""
+    want = plain(folder, tokens)[rows]
+    got = got.float().cpu()
+    if dtype == "float32":
+        torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4, msg=lambda m: f"{where}\n{m}")
+    else:
+        scale = float(want.pow(2).mean().sqrt())
+        per_row = (got - want).pow(2).mean(-1).sqrt() / scale
+        assert float(per_row.pow(2).mean().sqrt()) <= 0.06, f"{where}: rms error {float(per_row.pow(2).mean().sqrt()):.4f} of the scale"
+        slack = max(1, per_row.numel() // 20)
+        assert int((per_row > 0.1).sum()) <= slack, f"{where}: {int((per_row > 0.1).sum())} of {per_row.numel()} rows are off by a tenth of the scale"
+
+
+def tokens_of(vocab, n, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def stepped(stepper, slot, toks, cuts):
+    outs, at = [], 0
+    for c in list(cuts) + [len(toks)]:
+        if c > at:
+            outs.append(stepper.step([slot], [toks[at:c]], "all"))
+            at = c
+    stepper.check()
+    return torch.cat(outs)
+
+
+def make(folder, backend, max_tokens=2048, max_seqs=8):
+    device, dtype = backend
+    model = gf.load(folder, dtype=dtype, device=device)
+    cache = model.new_cache(max_tokens=max_tokens, max_seqs=max_seqs)
+    return model, cache, Stepper(model, cache)
+
+
+# ---- whole prompts, and the first tokens of a sequence ------------------------------------------------
+
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompts(folders, backend, name):
+    model, cache, st = make(folders[name], backend)
+    for n in (1, 2, 3, 6, 64, 71, 150):
+        toks = tokens_of(model.vocab_size, n, seed=n)
+        (slot,) = cache.begin(1)
+        got = st.step([slot], [toks], "all")
+        st.check()
+        cache.end([slot])
+        judge(got, folders[name], toks, slice(None), backend[1], f"{name}: prompt of {n}")
+
+
+def test_the_stream_after_every_layer(folders, backend):
+    """The residual stream behind each layer, not only the logits: a layer that is wrong by little does not hide
+    behind the layers after it."""
+    name = NAMES[0]
+    model, cache, st = make(folders[name], backend)
+    toks = tokens_of(model.vocab_size, 41, seed=8)
+    kept = []
+    model.after_layer = lambda x: kept.append(x.tensor().float().cpu().clone())
+    (slot,) = cache.begin(1)
+    st.step([slot], [toks], "all")
+    cache.end([slot])
+    model.after_layer = None
+    with open(os.path.join(folders[name], "config.json")) as f:
+        cfg = json.load(f)
+    _, want = pl.forward(cfg, load_file(os.path.join(folders[name], "model.safetensors")), toks, keep_layers=True)
+    assert len(kept) == want.shape[0]
+    for i, got in enumerate(kept):
+        tol = 3e-4 if backend[1] == "float32" else 0.05 * float(want[i].float().pow(2).mean().sqrt())
+        assert float((got - want[i].float()).pow(2).mean().sqrt()) <= tol, f"the stream behind layer {i}"
+
+
+def test_the_same_token_at_other_positions(folders, backend):
+    """The learned position vector: one token repeated gives other logits at every position, also across steps."""
+    name = NAMES[0]
+    model, cache, st = make(folders[name], backend)
+    for toks in ([7, 7, 7, 7, 7], [9], [9, 9]):
+        (slot,) = cache.begin(1)
+        got = stepped(st, slot, toks, range(1, len(toks)))
+        cache.end([slot])
+        judge(got, folders[name], toks, slice(None), backend[1], f"{name}: {toks}")
+
+
+# ---- prefill against token-by-token decoding, portions down to two tokens, long decoding ----------------
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("cuts", [
+    pytest.param(lambda n: range(1, n), id="token-by-token"),
+    pytest.param(lambda n: [20] + list(range(21, n)), id="prefill-then-long-decode"),
+    pytest.param(lambda n: [2, 4, 5, 9, 10, 64, 66, 69, 70, 72, 128, 130, 139, 141], id="portions"),
+    pytest.param(lambda n: [63, 65, 140], id="page-edges"),
+])
+def test_cuts_agree_with_the_whole(folders, backend, name, cuts):
+    model, cache, st = make(folders[name], backend)
+    toks = tokens_of(model.vocab_size, 143, seed=5)
+    (slot,) = cache.begin(1)
+    got = stepped(st, slot, toks, cuts(len(toks)))
+    cache.end([slot])
+    judge(got, folders[name], toks, slice(None), backend[1], f"{name}: cut prompt")
+    if backend[1] == "float32":
+        (slot,) = cache.begin(1)
+        whole = st.step([slot], [toks], "all")
+        cache.end([slot])
+        torch.testing.assert_close(got, whole, rtol=1e-4, atol=1e-4)
+
+
+def test_long_decoding(folders, backend):
+    """Windows pass over decoded tokens several times and the recurrent state carries over hundreds of steps."""
+    name = NAMES[0]
+    model, cache, st = make(folders[name], backend)
+    toks = tokens_of(model.vocab_size, 310, seed=9)
+    (slot,) = cache.begin(1)
+    got = stepped(st, slot, toks, [5] + list(range(6, len(toks))))
+    cache.end([slot])
+    judge(got[-40:], folders[name], toks, slice(len(toks) - 40, len(toks)), backend[1], f"{name}: the last of 305 decode steps")
+
+
+# ---- batches of unequal requests against each alone; slots, pages and state used again ------------------
+
+@pytest.mark.parametrize("name", NAMES)
+def test_batches_and_reuse(folders, backend, name):
+    model, cache, st = make(folders[name], backend, max_tokens=1024, max_seqs=4)
+    V = model.vocab_size
+    for turn in range(3):                                  # the later rounds get slots, pages and state that were used before
+        lens = [[70, 3, 131], [1, 66, 9, 20], [129, 2]][turn]
+        reqs = [tokens_of(V, n + 6, seed=100 * turn + n) for n in lens]
+        slots = cache.begin(len(reqs))
+        rows = {i: [] for i in range(len(reqs))}
+        out = st.step(slots, [r[:n] for r, n in zip(reqs, lens)], "all")       # packed prefill
+        at = 0
+        for i, n in enumerate(lens):
+            rows[i].append(out[at:at + n])
+            at += n
+        live = list(range(len(reqs)))
+        for k in range(6):                                   # decode together; the shorter ones (by index) leave early
+            live = [i for i in live if not (k >= 2 + 2 * i and i < len(reqs) - 1)]
+            out = st.step([slots[i] for i in live], [[reqs[i][lens[i] + k]] for i in live], "all")
+            for j, i in enumerate(live):
+                rows[i].append(out[j:j + 1])
+        st.check()
+        cache.end(slots)
+        for i, r in enumerate(reqs):
+            got = torch.cat(rows[i])
+            judge(got, folders[name], r, slice(0, got.shape[0]), backend[1], f"{name}: pass {turn}, request {i}")
+    assert cache.slots.n_free == cache.n_slots and all(g.pages.n_free == cache.n_pages for g in cache.kv_groups)
+
+
+# ---- greedy generation through the library's entry point and scheduler -----------------------------------
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation(folders, backend, name):
+    device, dtype = backend
+    model = gf.load(folders[name], dtype=dtype, device=device)
+    prompts = [tokens_of(model.vocab_size, n, seed=7 * n) for n in (5, 1, 68, 12)]
+    seqs, stats = gf.generate(model, prompts, 9, temperature=0.0, batch_size=3)
+    assert stats.batches == 2 and [len(s) for s in seqs] == [len(p) + 9 for p in prompts]
+    for p, s in zip(prompts, seqs):
+        assert s[:len(p)] == p
+        logits = plain(folders[name], s[:-1])
+        for j in range(len(p) - 1, len(s) - 1):
+            margin = 1e-3 if dtype == "float32" else 0.1 * float(logits[j].pow(2).mean().sqrt()) + 0.05
+            assert logits[j, s[j + 1]] >= logits[j].max() - margin, f"{name}: token {j + 1} is not the plain argmax"
+
+
+# ---- what the model asks of the cache -----------------------------------------------------------------------
+
+def test_cache_entries(folders, backend):
+    model, cache, st = make(folders[NAMES[1]], backend)
+    needs = model.cache_needs()
+    assert -1 in needs and needs[-1].kv is None and needs[-1].state is None          # positions need no state
+    # layer 0: sink attention (keys and values) beside the delta rule (state and 4 carried rows of its convolutions)
+    assert needs[0].kv.n_kv == 1 and needs[0].kv.head_dim == 24 and needs[0].kv.v_head_dim == 40 and needs[0].kv.window == 1
+    assert needs[0].state.shape == (16 * 16 + 4 * (16 + 16 + 16),)
+    assert needs[1].kv is not None and needs[1].state is None                        # one tap: nothing is carried
+    assert needs[2].kv is None and needs[2].state.shape == (4 * 6 * 8,)              # a reader: only its queries' carried rows
+    assert needs[4].kv is None and needs[4].state.shape == (3 * 2 * 32,)
+    sched = model.spec.schedule
+    assert [e.kv_from for e in sched] == [None, None, 1, None, 3] and all(e.owns_cache for e in sched)
+
+
+# ---- configuration and weights ------------------------------------------------------------------------------
+
+def test_config_errors_name_the_key():
+    cfg = gf.config_from_name("lomusun-tiny-a")
+    for path, value, word in [(("layers", 0, "type"), "mamba2", "type"), (("layers", 0, "mixer", "kv_heads"), 3, "kv_heads"),
+                              (("layers", 2, "mixer", "kv_from"), 1, "kv_from"), (("layers", 2, "mixer", "kv_from"), 2, "kv_from"),
+                              (("layers", 2, "mixer", "dim"), 16, "dim"), (("layers", 0, "mlp", "kind"), "dense", "mlp"),
+                              (("layers", 0, "mlp", "router", "top"), 6, "experts"), (("layers", 1, "mixer", "left", "mask"), 5, "mask"),
+                              (("layers", 1, "mixer", "right", "conv"), 0, "conv"), (("norm",), 1e-5, "norm"),
+                              (("max_positions",), 0, "max_positions"), (("layers", 0, "mlp", "expert", "limit"), 0.0, "limit")]:
+        bad = json.loads(json.dumps(cfg))
+        node = bad
+        for k in path[:-1]:
+            node = node[k]
+        node[path[-1]] = value
+        with pytest.raises(gf.ConfigError, match=word):
+            gf.load(bad, device="cpu", random_weights=True)
+
+
+def test_weights_turntrip_and_one_error(folders, tmp_path):
+    from safetensors.torch import save_file
+    name = NAMES[0]
+    model = gf.load(folders[name], dtype="bfloat16", device="cpu")
+    gf.save_folder(model, str(tmp_path / "again"))
+    a, b = load_file(os.path.join(folders[name], "model.safetensors")), load_file(str(tmp_path / "again" / "model.safetensors"))
+    assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+    assert "l2.mix.k" not in a and "l2.mix.v.conv" not in a and "l2.mix.q.conv" in a         # a reader has queries only
+    broken = dict(a)
+    del broken["l1.mix.left.sink"]
+    broken["l0.mix.q.conv"] = torch.zeros(5, 3)
+    broken["l2.mix.k"] = torch.zeros(1)
+    os.makedirs(tmp_path / "broken")
+    save_file(broken, str(tmp_path / "broken" / "model.safetensors"))
+    with open(tmp_path / "broken" / "config.json", "w") as f:
+        json.dump(gf.config_from_name(name), f)
+    with pytest.raises(gf.WeightError) as e:
+        gf.load(str(tmp_path / "broken"), device="cpu")
+    assert e.value.missing == ["l1.mix.left.sink"] and e.value.unexpected == ["l2.mix.k"] and e.value.wrong_shape[0][0] == "l0.mix.q.conv"
+
+
+def test_table_rows_come_from_the_tensor_shape(folders, tmp_path, plain_kernels):
+    """config.json need not name the rows of a distance table: the checkpoint's shape does."""
+    from safetensors.torch import save_file
+    name = NAMES[0]
+    w = load_file(os.path.join(folders[name], "model.safetensors"))
+    g = torch.Generator().manual_seed(1)
+    w["l0.mix.rel"] = torch.randn(9, 4, generator=g).to(torch.bfloat16)
+    os.makedirs(tmp_path / "m")
+    save_file(w, str(tmp_path / "m" / "model.safetensors"))
+    cfg = gf.config_from_name(name)
+    del cfg["layers"][0]["mixer"]["bias_rows"]
+    with open(tmp_path / "m" / "config.json", "w") as f:
+        json.dump(cfg, f)
+    model = gf.load(str(tmp_path / "m"), dtype="float32", device="cpu")
+    toks = tokens_of(cfg["vocab"], 60, seed=2)
+    cache = model.new_cache(max_tokens=64, max_seqs=1)
+    got = Stepper(model, cache).step(cache.begin(1), [toks], "all")
+    torch.testing.assert_close(got, pl.forward(cfg, w, toks).float(), rtol=3e-4, atol=3e-4)
+
+
+# ---- the trace program and the command line as a user runs them ----------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run(folders, tmp_path, dtype):
+    name = NAMES[1]
+    folder = folders[name]
+    V = gf.config_from_name(name)["vocab"]
+    reqs = traces.make_requests(V, [40, 3, 77, 65], seed=3)
+    for cut, steps in (("whole", traces.whole(reqs)), ("stepped", traces.stepped(reqs)), ("batched", traces.batched(reqs, 3))):
+        out_dir = str(tmp_path / cut)
+        cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
+               "--max-tokens", str(traces.peak_tokens(steps))]
+        proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+        try:
+            for s in steps:
+                proc.stdin.write(json.dumps(s) + "\n")
+                proc.stdin.flush()
+                assert proc.stdout.readline().strip() == f"done {s['step']}"
+            proc.stdin.close()
+            assert proc.wait(timeout=120) == 0
+        finally:
+            if proc.poll() is None:
+                proc.kill()
+        outputs = {}
+        for s in steps:
+            wanted = sum(len(e["want"]) for e in s["entries"])
+            if wanted:
+                outputs[s["step"]] = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(wanted, V)
+        by_request = {}
+        for (rid, j), row in traces.collect(steps, outputs, V).items():
+            by_request.setdefault(rid, []).append((j, row))
+        for rid, rows in by_request.items():
+            rows.sort(key=lambda x: x[0])
+            got = torch.from_numpy(np.stack([r for _, r in rows]))
+            judge(got, folder, reqs[rid], [j for j, _ in rows], dtype, f"{cut}: {rid}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cli_greedy(folders, tmp_path, dtype):
+    from test_cli_gpu import read_lines, run_cli
+    name = NAMES[1]
+    out = tmp_path / "tokens.jsonl"
+    r = run_cli("--checkpoint_path", folders[name], "--prompt", "4,13", "--max_new_tokens", "7", "--temperature", "0",
+                "--dtype", dtype, "--output", str(out))
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = read_lines(out)
+    assert [len(x["prompt"]) for x in rows] == [4, 13]
+    for x in rows:
+        assert len(x["tokens"]) == 7
