@@ -303,6 +303,10 @@ struct RopeSource {
     // two options of the mask and the softmax that travel with this struct (both off when zero / null):
     int chunk;                // a query sees only the keys of its own block of `chunk` positions (blocks from position 0)
     const float* sink;        // [H], 32-bit: exp(sink_h) joins the denominator of head h and has no value
+    // a bias on the scaled score by head and distance n = query position - key position (both off when null):
+    const float* bias;        // [bias_len][H], 32-bit: row min(n, bias_len - 1) is added
+    int bias_len;
+    const float* slopes;      // [H], 32-bit: slopes[h] * n is taken off
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
@@ -660,7 +664,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 int j = p * PAGE + warp * 16 + n * 8 + 2 * t4 + e;
-                float x = (j >= lo && j <= pos) ? sc[n][e] * scale_log2e : -INFINITY;
+                const bool seen = j >= lo && j <= pos;
+                float x = seen ? sc[n][e] * scale_log2e : -INFINITY;
+                if (seen && gq < rep) {
+                    const int head = g * rep + gq;
+                    if (rs.bias != nullptr) x = fmaf(rs.bias[(size_t)min(pos - j, rs.bias_len - 1) * H + head], 1.4426950408889634f, x);
+                    if (rs.slopes != nullptr) x = fmaf(-rs.slopes[head] * 1.4426950408889634f, (float)(pos - j), x);
+                }
                 v[n * 2 + e] = x;
                 mx = fmaxf(mx, x);
             }
@@ -888,11 +898,33 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
                                   lengths, n_seqs, n_tokens, H, G, d, scale, window, 0, nullptr, splits, scratch, status, stream);
 }
 
+GFB_API int gfb_attn_decode_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, const float* bias, int bias_len, const float* slopes, int splits,
+                                   float* scratch, int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_decode_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                    int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                    const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                    int chunk, const float* sink, int splits, float* scratch, int* status, cudaStream_t stream) {
+    return gfb_attn_decode_biased(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                                  lengths, n_seqs, n_tokens, H, G, d, scale, window, chunk, sink, nullptr, 0, nullptr, splits, scratch,
+                                  status, stream);
+}
+
+// The same with a bias on the scaled score that depends on the head and the distance n = query position - key position:
+// `bias` (float32 [bias_len][H] or null: row min(n, bias_len - 1) is added) and `slopes` (float32 [H] or null:
+// slopes[h] * n is taken off).  head_dim 64 or 128 only.
+GFB_API int gfb_attn_decode_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, const float* bias, int bias_len, const float* slopes, int splits,
+                                   float* scratch, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if ((bias != nullptr || slopes != nullptr) && d != 64 && d != 128)
+        return gfb_fail("gfb_attn_decode_biased: a distance bias needs head_dim 64 or 128, got %d", d);
+    if (bias != nullptr && bias_len < 1) return gfb_fail("gfb_attn_decode_biased: a distance table of %d rows", bias_len);
     if ((chunk > 0 || sink != nullptr) && d != 64 && d != 128)
         return gfb_fail("gfb_attn_decode_masked: a block mask or a sink needs head_dim 64 or 128, got %d", d);
     if (page_size != PAGE) return gfb_fail("gfb_attn_decode: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
@@ -918,6 +950,9 @@ GFB_API int gfb_attn_decode_masked(const void* q, void* out, void* k_pool, void*
         RopeSource rs{};
         rs.chunk = chunk;
         rs.sink = sink;
+        rs.bias = bias;
+        rs.bias_len = bias_len;
+        rs.slopes = slopes;
         e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, rs, 0);
         if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     } else {

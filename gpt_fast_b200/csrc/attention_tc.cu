@@ -257,6 +257,47 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// A bias on the score that depends on the head and on the distance n = query position - key position only, in units of
+// the raw score (the bias divided by the score scale), so that it joins the score before scale and exponential.
+//   table   null, or four copies [4][H][len] of a per-head array in which ascending entries belong to ascending keys:
+//           entry u holds the bias at distance top - u; the first entries (distances beyond the last one the table tells
+//           apart) all hold the far value, the entries beyond `top` (keys behind the query, masked anyway) are padding.
+//           Copy s is the array moved down by s entries, so the 16-byte loads of a thread, whose first entry can have
+//           any index, are aligned in the copy s = index mod 4.
+//   slopes  null, or [H]: slopes[h] * n is taken off.
+struct DistanceBias {
+    const float* table;
+    int len, top;
+    const float* slopes;
+};
+
+// v[c][i] belongs to key key0 + 32 c + i.
+template <int NC>
+__device__ __forceinline__ void add_distance_bias(float (&v)[NC][32], const DistanceBias& db, int H, int head, int row_pos, int key0) {
+    if (db.table != nullptr) {
+        // A block whose keys all lie beyond the table's reach starts below entry 0: the first NC * 32 entries hold the
+        // far value, so the clamp reads the right numbers.  The upper clamp only moves loads of masked keys.
+        const int u0 = min(max(db.top - row_pos + key0, 0), db.len - NC * 32 - 4);
+        const int s = u0 & 3;
+        const float4* src = reinterpret_cast<const float4*>(db.table + ((size_t)s * H + head) * db.len + (u0 - s));
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 t = __ldg(src + c * 8 + (i >> 2));
+                v[c][i] += t.x; v[c][i + 1] += t.y; v[c][i + 2] += t.z; v[c][i + 3] += t.w;
+            }
+    }
+    if (db.slopes != nullptr) {
+        const float sl = __ldg(db.slopes + head);
+        const float at0 = sl * (float)(key0 - row_pos);            // exact: distances are far below 2^24
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[c][i] += fmaf(sl, (float)(c * 32 + i), at0);
+    }
+}
+
 // The first key the query at `pos` sees: the window's edge, or the start of its block of `chunk` positions
 // (blocks counted from position 0), whichever is later.
 __device__ __forceinline__ int first_key(int pos, int window, int chunk) {
@@ -315,7 +356,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
                        GfbBatch b, int H, int G, float scale_log2e, int window, int chunk, const float* __restrict__ sink,
-                       int n_x, int* status) {
+                       DistanceBias db, int n_x, int* status) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 0) { prefetch_map(&map_q); prefetch_map(&map_k); prefetch_map(&map_v); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -505,6 +546,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[c][i] = __uint_as_float(raw[c][i]);
+                if (db.table != nullptr || db.slopes != nullptr)
+                    add_distance_bias<2>(v, db, H, t.g * rep + (r - tq * rep), row_pos, key0);
                 if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
 #pragma unroll
                     for (int c = 0; c < 2; c++)
@@ -655,7 +698,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ page_table, int max_pages, int n_pages_pool,
                         GfbBatch b, int H, int G, float scale_log2e, int window, int chunk, const float* __restrict__ sink,
-                        int* status) {
+                        DistanceBias db, int* status) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 0) { prefetch_map(&map_q); prefetch_map(&map_k); prefetch_map(&map_v); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -861,6 +904,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < last_lo || window > 0 || nq[x] < TQ;
             float v[4][32];
             tmem_ld_row128(lane_base + col_s, v);
+            if (db.table != nullptr || db.slopes != nullptr)
+                add_distance_bias<4>(v, db, H, g * rep + (r - tq * rep), row_pos, key0);
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < 4; c++)
@@ -994,11 +1039,35 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
 
 // The same with a block mask (chunk > 0: a query sees only the keys of its own block of `chunk` positions, blocks
 // counted from position 0) and a sink (float32 [H] or null: exp(sink_h) joins the softmax denominator of head h).
+GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, const float* bias, int bias_len, int bias_top,
+                                       const float* slopes, int tiles, int max_blocks, int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                        int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                        const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                        int chunk, const float* sink, int tiles, int max_blocks, int* status, cudaStream_t stream) {
+    return gfb_attn_prefill_tc_biased(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                                      lengths, n_seqs, n_tokens, H, G, d, scale, window, chunk, sink, nullptr, 0, 0, nullptr, tiles,
+                                      max_blocks, status, stream);
+}
+
+// The same with a bias by head and distance in units of the raw score (the bias divided by `scale`): `bias` null or
+// float32 [4][H][bias_len], the four moved copies of the per-head array that `DistanceBias` describes, with distance 0 at
+// entry bias_top; `slopes` null or float32 [H].
+GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, const float* bias, int bias_len, int bias_top,
+                                       const float* slopes, int tiles, int max_blocks, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (bias != nullptr && (bias_len % 4 || bias_len < 128 + 4 + 384 || bias_top < 127 || bias_top + 384 >= bias_len
+                            || (reinterpret_cast<uintptr_t>(bias) & 15)))
+        return gfb_fail("gfb_attn_prefill_tc: a distance array of %d entries with distance 0 at %d (128 far entries ahead of the table, "
+                        "384 behind distance 0, a multiple of 4, 16-byte aligned)", bias_len, bias_top);
+    const DistanceBias db{bias, bias_len, bias_top, slopes};
     if (page_size != PAGE || (d != 64 && d != 128))
         return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim 64 or 128, got %d and %d", PAGE, page_size, d);
     if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
@@ -1053,7 +1122,7 @@ GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, v
         }
         dim3 grid((n_tokens + 2 * TQ - 1) / (2 * TQ) + n_seqs, G);
         e = gfb_launch(attn_prefill_tc2_kernel, grid, dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, status);
+                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, status);
     } else {
         size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
         static bool configured = false;
@@ -1069,10 +1138,10 @@ GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, v
         if (blocks > cap) blocks = cap;
         if (d == 128)
             e = gfb_launch(attn_prefill_tc_kernel<128>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status);
         else
             e = gfb_launch(attn_prefill_tc_kernel<64>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status);
     }
     return gfb_check(e, "gfb_attn_prefill_tc");
 }

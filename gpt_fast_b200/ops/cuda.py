@@ -81,6 +81,7 @@ class CudaKernels:
         self._status = None
         self.trace = None                  # a list: (label, start event, stop event) of every launch is appended
         self._label = None                 # what the next launch is called in the trace (default: the entry point)
+        self._bias_cache = {}              # distance biases in the tensor-core prefill kernel's layout, by table
 
     def _f(self, lib: str, name: str):
         key = (lib, name)
@@ -670,10 +671,11 @@ class CudaKernels:
                               c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
                               c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), c_int(splits),
                               _ptr(scratch), _ptr(batch.status), _stream())
-        if (not values_in_keys and not biased and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
-                and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
-            # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for
-            return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink)
+        if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+                and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256)) and (not biased or scale > 0)):
+            # the tensor-core kernels; a block mask, a sink or a distance bias only at the head sizes they are built for
+            return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink,
+                                        bias=bias, slopes=slopes)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
                    c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), c_int(1 if values_in_keys else 0),
@@ -682,12 +684,45 @@ class CudaKernels:
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)
 
+    # entries of a distance array ahead of the table (all the far value) and behind distance 0 (keys behind the query)
+    BIAS_FAR_ENTRIES, BIAS_BEHIND_ENTRIES = 128, 384
+
+    def _distance_arrays(self, bias, slopes, scale):
+        """A distance bias in the form the tensor-core prefill kernel reads, made once per table and kept: everything divided
+        by the score scale (the kernel adds it to the raw score); the table [rows, H] as four copies [4, H, len] of a
+        per-head array in which entry `top` - n holds distance n (distances beyond the table the last row's value, entries
+        beyond `top` zeros), copy s moved down by s entries so that 16-byte loads from any entry are aligned in one copy."""
+        key = (bias.data_ptr() if bias is not None else 0, slopes.data_ptr() if slopes is not None else 0, float(scale))
+        hit = self._bias_cache.get(key)
+        if hit is not None and hit[0] is bias and hit[1] is slopes:
+            return hit[2:]
+        arrays, length, top = None, 0, 0
+        if bias is not None:
+            rows = bias.shape[0]
+            top = rows - 1 + self.BIAS_FAR_ENTRIES
+            length = -(-(top + 1 + self.BIAS_BEHIND_ENTRIES) // 4) * 4
+            n = top - torch.arange(length + 3, device=bias.device)                        # the distance of every entry
+            one = (bias / scale)[n.clamp(0, rows - 1)] * (n >= 0).unsqueeze(1)            # [len + 3, H]
+            arrays = torch.stack([one[s:s + length].t() for s in range(4)]).contiguous()  # [4, H, len]
+        per_head = None if slopes is None else (slopes / scale).contiguous()
+        if len(self._bias_cache) > 256:
+            self._bias_cache.clear()
+        self._bias_cache[key] = (bias, slopes, arrays, length, top, per_head)
+        return arrays, length, top, per_head
+
     def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0,
-                        max_blocks=0, chunk=None, sink=None):
+                        max_blocks=0, chunk=None, sink=None, bias=None, slopes=None):
         T = batch.n_tokens
         if prefill is None:
             prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
         if prefill and head_dim in (64, 128) and n_head // n_kv <= 8:
+            if bias is not None or slopes is not None:
+                arrays, length, top, per_head = self._distance_arrays(bias, slopes, scale)
+                self._call("attention_tc", "gfb_attn_prefill_tc_biased", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                           c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0),
+                           _ptr(sink), _ptr(arrays), c_int(length), c_int(top), _ptr(per_head), c_int(tiles), c_int(max_blocks),
+                           _ptr(batch.status), _stream())
+                return
             self._call("attention_tc", "gfb_attn_prefill_tc_masked", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
                        c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
                        c_int(tiles), c_int(max_blocks), _ptr(batch.status), _stream())
@@ -701,6 +736,12 @@ class CudaKernels:
         scratch = None
         if splits > 1:
             scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+        if bias is not None or slopes is not None:
+            self._call("attention_bf16", "gfb_attn_decode_biased", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
+                       _ptr(bias), c_int(bias.shape[0] if bias is not None else 0), _ptr(slopes), c_int(splits), _ptr(scratch),
+                       _ptr(batch.status), _stream())
+            return
         self._call("attention_bf16", "gfb_attn_decode_masked", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
                    c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
                    c_int(splits), _ptr(scratch), _ptr(batch.status), _stream())
