@@ -359,6 +359,7 @@ def step_shares(gf, torch, ops, model, prompts, decode):
     for label, ms in ops.trace_times(rec):
         kind = label.split(" ")[0] + (" " + label.split(" ")[-1] if label.startswith("linear") else "")
         out[kind] = out.get(kind, 0.0) + ms
+    stepper.check()                     # a bounded wait that ran out would show as a kernel of seconds: fail instead
     cache.end(slots)
     return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
 

@@ -27,7 +27,17 @@
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_GELU = 4, EPI_RELU2 = 7 };   // GELU: store gelu(acc), the exact (erf) form, as bfloat16; RELU2: store max(acc, 0)^2
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_GELU = 4, EPI_RELU2 = 7, EPI_GLU_CLAMP = 8 };   // GELU: store gelu(acc), the exact (erf) form, as bfloat16; RELU2: store max(acc, 0)^2; GLU_CLAMP: see Groups
+
+// A product whose row tiles use different weight matrices (a mixture of experts with its rows sorted by expert): row tile i
+// multiplies with the rows [tile_group[i] * group_rows, + N) of the weight matrix; a tile whose entry is negative has no rows.
+// The clamped gated epilogue over alternating gate/up columns stores g * sigmoid(alpha g) * (u + shift),
+// g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: no clamp).
+struct Groups {
+    const int* tile_group;
+    int group_rows;
+    float limit, alpha, shift;
+};
 
 // what a storing epilogue does to an accumulator value before it rounds it
 template <int EPI>
@@ -221,6 +231,11 @@ __device__ __forceinline__ bool epilogue_warps_all(bool flag) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
+__device__ __forceinline__ float glu_clamp(float g, float u, const Groups& gp) {
+    if (gp.limit > 0.f) { g = fminf(g, gp.limit); u = fminf(fmaxf(u, -gp.limit), gp.limit); }
+    return g * (1.0f / (1.0f + expf(-gp.alpha * g))) * (u + gp.shift);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -235,7 +250,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // together.  Only __syncwarp is needed: a warp reads back what it wrote itself.
 template <int BN, int EPI, typename TO>
 __device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int q, int lane, TO* out, int row0, int col0,
-                                              int R, int N, int ldo) {
+                                              int R, int N, int ldo, const Groups& gp) {
     constexpr int SP = BN + 4;
     float* mine = stage + (size_t)(q * 32 + lane) * SP;
 #pragma unroll 1
@@ -287,6 +302,20 @@ __device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int 
                 *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(row0 + q * 32 + rr) * ldo + ((col0 + c) >> 1)) = pk;
             }
         }
+    } else if (EPI == EPI_GLU_CLAMP) {
+        // the same walk with the clamped gate; N % 8 == 0 keeps a lane's 8 columns inside the matrix or outside it
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr++) {
+            int c = lane * 8;
+            if (c < BN && col0 + c < N) {
+                const float* a = stage + (size_t)(q * 32 + rr) * SP + c;
+                float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
+                uint2 pk;
+                pk.x = pack_bf16(glu_clamp(lo.x, lo.y, gp), glu_clamp(lo.z, lo.w, gp));
+                pk.y = pack_bf16(glu_clamp(hi.x, hi.y, gp), glu_clamp(hi.z, hi.w, gp));
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(row0 + q * 32 + rr) * ldo + ((col0 + c) >> 1)) = pk;
+            }
+        }
     } else if (sizeof(TO) == 4) {
         constexpr int PASSES = BN >= 128 ? BN / 128 : 1;
 #pragma unroll 2
@@ -317,11 +346,12 @@ __device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int 
 // ---- the kernel ---------------------------------------------------------------------
 // X: [R, K] rows of the MMA; Y: [Cc, K] columns of the MMA.  SWAP = false: rows are
 // tokens, out[r * ldo + c]; SWAP = true: rows are weight rows, out[c * ldo + r].
-template <int BN, bool SWAP, int EPI, typename TO>
+template <int BN, bool SWAP, int EPI, typename TO, bool GROUPED = false>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                TO* __restrict__ out, float* __restrict__ partial, int R, int Cc, int K, int ldo,
-               int kb_per_split, int stages, int* status) {
+               int kb_per_split, int stages, int* status, const Groups gp) {
+    static_assert(!(GROUPED && SWAP), "groups of row tiles exist in the normal orientation only");
     constexpr int Y_TILE_BYTES = BN * BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ uint8_t smem_raw[];
@@ -350,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // Weights are written by no kernel: the ring is filled with weight tiles at once, before the block's tensor
         // memory is there and before the wait for the previous kernel (no other thread touches the barriers before
         // the block's barrier below).
-        const int n_pre = min(stages, nkb);
+        const int n_pre = GROUPED ? 0 : min(stages, nkb);   // which weights a grouped tile reads, the previous kernel says
         for (int i = 0; i < n_pre; i++) {                   // fresh barriers: every stage is free
             uint32_t full = smem_u32(&bars->full[i]);
             mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
@@ -374,13 +404,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     gfb_pdl_launch();
     if (!(warp == 0 && lane == 0)) gfb_pdl_wait();
 
-    if (warp == 0) {
+    // a grouped tile: its weights' first row, or nothing to do at all (every role skips its part, the block frees its
+    // tensor memory and ends)
+    int group = 0;
+    if constexpr (GROUPED) {
+        if (warp == 0 && lane == 0) gfb_pdl_wait();
+        group = gp.tile_group[blockIdx.x];
+    }
+    const bool idle = GROUPED && group < 0;
+    const int ycol0 = GROUPED ? group * gp.group_rows + col0 : col0;
+
+    if (idle) {
+    } else if (warp == 0) {
         if (lane == 0) {
             const int n_pre = min(stages, nkb);             // their weight halves are on their way already
             const uint64_t pol = l2_evict_first_policy();
-            gfb_pdl_wait();
+            if (!GROUPED) gfb_pdl_wait();
             for (int i = 0; i < n_pre; i++) {
                 uint32_t full = smem_u32(&bars->full[i]);
+                if (GROUPED) {
+                    mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                    tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, ycol0, full);
+                }
                 if (SWAP) tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
                 else tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
             }
@@ -392,7 +437,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
                 if (SWAP) tma_load_2d_hint(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full, pol);
                 else tma_load_2d(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
-                tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
+                tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, ycol0, full);
             }
         }
     } else if (warp == 1) {
@@ -424,7 +469,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if constexpr (!SWAP) {
                 if (ok && row0 + q * 32 < R)
                     epilogue_rows<BN, EPI == EPI_PARTIAL ? EPI_STORE : EPI, TO>(reinterpret_cast<float*>(aligned), taddr, q, lane,
-                                                                                out, row0, col0, R, Cc, ldo);
+                                                                                out, row0, col0, R, Cc, ldo, gp);
             } else {
             // Up to 64 accumulator columns (tokens) a round, brought from tensor memory by one load.
             constexpr int GROUP = BN < 64 ? BN : 64;
@@ -1073,8 +1118,26 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* parti
         configured = smem;
     }
     dim3 grid((R + BM - 1) / BM, (Cc + BN - 1) / BN, splits);
-    cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, partial, R, Cc, K, ldo, kb_per_split, stages, status);
+    cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, partial, R, Cc, K, ldo, kb_per_split, stages, status,
+                               Groups{nullptr, 0, 0.f, 0.f, 0.f});
     return gfb_check(e, "gfb_gemm_tc");
+}
+
+template <int BN, int EPI, typename TO>
+int launch_grouped(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, int Cc, int K, int ldo, int stages, int* status,
+                   const Groups& gp, cudaStream_t stream) {
+    auto kern = gemm_tc_kernel<BN, false, EPI, TO, true>;
+    size_t smem = smem_bytes(BN, stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("gfb_gemm_tc_grouped: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    dim3 grid((R + BM - 1) / BM, (Cc + BN - 1) / BN, 1);
+    cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, (float*)nullptr, R, Cc, K, ldo,
+                               (K + BK - 1) / BK, stages, status, gp);
+    return gfb_check(e, "gfb_gemm_tc_grouped");
 }
 
 size_t persistent_smem_bytes(int stages) {
@@ -1240,4 +1303,28 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         return gfb_check(e, "gfb_gemm_tc (split reduce)");
     }
     return 0;
+}
+
+// Row tiles of 128 rows that each use one of `groups` weight matrices: out[r] = A[r] * W[tile_group[r / 128]]^T for
+// A [rows, K] (rows a multiple of 128), W [groups, N, K]; a tile whose entry is negative is skipped.  epi: EPI_STORE
+// with out float32 [rows, N], or EPI_GLU_CLAMP with out bfloat16 [rows, N / 2] from alternating gate/up rows of W.
+GFB_API int gfb_gemm_tc_grouped(const void* A, const void* W, void* out, int out_dt, int rows, int groups, int N, int K, int epi,
+                                const int* tile_group, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0 || groups <= 0) return 0;
+    if (rows % BM) return gfb_fail("gfb_gemm_tc_grouped: %d rows are not whole tiles of %d", rows, BM);
+    if (K <= 0 || K % 8) return gfb_fail("gfb_gemm_tc_grouped: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (N % 8) return gfb_fail("gfb_gemm_tc_grouped: N = %d must be a multiple of 8", N);
+    if (epi == EPI_GLU_CLAMP && N % 16) return gfb_fail("gfb_gemm_tc_grouped: the gated epilogue needs N %% 16 == 0, got %d", N);
+    if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc_grouped: operands must be 16-byte aligned");
+    if ((long)groups * N > 0x7fffffffL) return gfb_fail("gfb_gemm_tc_grouped: %d matrices of %d rows exceed a tensor map's coordinates", groups, N);
+    constexpr int GBN = 128, STAGES = 6;
+    CUtensorMap mx, my;
+    if (make_map(&mx, A, rows, K, BM)) return 1;
+    if (make_map(&my, W, groups * N, K, GBN)) return 1;
+    const Groups gp{tile_group, N, limit, alpha, shift};
+    if (epi == EPI_GLU_CLAMP && out_dt == GFB_BF16)
+        return launch_grouped<GBN, EPI_GLU_CLAMP, __nv_bfloat16>(mx, my, out, rows, N, K, N / 2, STAGES, status, gp, stream);
+    if (epi == EPI_STORE && out_dt == GFB_F32)
+        return launch_grouped<GBN, EPI_STORE, float>(mx, my, out, rows, N, K, N, STAGES, status, gp, stream);
+    return gfb_fail("gfb_gemm_tc_grouped: unsupported epilogue %d / output type %d", epi, out_dt);
 }

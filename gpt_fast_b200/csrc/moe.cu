@@ -12,9 +12,11 @@
 // Two forms of the expert products.  Few tokens (a decode step): a warp per output number streams the weight row once,
 // 16 bytes per lane and load, the token's input staged in shared memory.  Many tokens (a prompt): the pairs are sorted by
 // expert (gfb_moe_plan: each expert's rows padded to whole tiles) and the products run tile by tile, each tile with its
-// expert's weights (gfb_moe_glu_tiles, gfb_moe_down_tiles), the rows' results scattered back to pair order.  In both
-// forms a number is one ascending sum over k in 32-bit (per lane and then a fixed butterfly, or per thread), so a token's
-// result does not depend on what else is in the batch.
+// expert's weights, the rows' results brought back to pair order.  The tiles run on the tensor cores (bfloat16: the
+// grouped product of the tcgen05 library between gfb_moe_gather_rows and gfb_moe_combine_rows, tiles of 128 rows) or on
+// CUDA cores (32-bit, and shapes the tensor-core tiles do not take: moe_tiles_simt_kernel, tiles of 64 rows).  In every
+// form a number is one sum over k in 32-bit in an order that does not depend on the other rows, so a token's result does
+// not depend on what else is in the batch.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -327,6 +329,64 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     float acc = 0.f;
     for (int r = 0; r < top; r++) acc = fmaf(weights[t * top + r], y[((size_t)t * top + r) * D + c], acc);
     x[i] += acc;
+}
+
+// ------------------------------------------------------------------------------------ around the tensor-core tiles ----
+// The tensor cores' tiles read their rows where TMA finds them: side by side in the sorted order.  hs[row] = h[row_pair[row] / top]
+// (zeros for padding rows), 16 bytes per thread and step.
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const uint4* __restrict__ h, const int* __restrict__ row_pair, uint4* __restrict__ hs, int top, int vec_per_row) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int row = blockIdx.x;
+    const int p = row_pair[row];
+    const uint4* src = p < 0 ? nullptr : h + (size_t)(p / top) * vec_per_row;
+    uint4* dst = hs + (size_t)row * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// h [T, D] bfloat16 with D % 8 == 0 -> hs [rows, D] in the plan's sorted order
+GFB_API int gfb_moe_gather_rows(const void* h, const int* row_pair, void* hs, int rows, int top, int D, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (D % 8 || ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(hs)) & 15))
+        return gfb_fail("gfb_moe_gather_rows: rows of %d bfloat16 numbers are not whole 16-byte pieces", D);
+    cudaError_t e = gfb_launch(moe_gather_rows_kernel, dim3((unsigned)rows), dim3(128), 0, stream, (const uint4*)h, row_pair, (uint4*)hs, top,
+                               D / 8);
+    return gfb_check(e, "gfb_moe_gather_rows");
+}
+
+// x[t] += sum_r weights[t, r] * y[pair_row[t * top + r]] in ascending r; y in the plan's sorted order, D % 4 == 0
+__global__ void __launch_bounds__(256)
+moe_combine_rows_kernel(const float4* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
+                        float4* __restrict__ x, int top, int vec_per_row, long n) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long t = i / vec_per_row;
+    const int c = (int)(i - t * vec_per_row);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < top; r++) {
+        const int row = pair_row[t * top + r];
+        if (row < 0) continue;
+        const float w = weights[t * top + r];
+        const float4 v = y[(size_t)row * vec_per_row + c];
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+    float4 o = x[i];
+    o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+    x[i] = o;
+}
+
+GFB_API int gfb_moe_combine_rows(const float* y, const int* pair_row, const float* weights, float* x, int T, int top, int D,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D % 4 || ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15))
+        return gfb_fail("gfb_moe_combine_rows: rows of %d floats are not whole 16-byte pieces", D);
+    const long n = (long)T * (D / 4);
+    cudaError_t e = gfb_launch(moe_combine_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float4*)y, pair_row,
+                               weights, (float4*)x, top, D / 4, n);
+    return gfb_check(e, "gfb_moe_combine_rows");
 }
 
 // h [T, D], w13 [E, 2F, D], act [rows, F] of type dt.  tiles = 0: the few-token form, act in pair order (rows = T * top);

@@ -496,8 +496,11 @@ class CudaKernels:
                    c_int(gate_off), c_int(group), _stream())
 
     # -- mixture of experts ------------------------------------------------------------------
-    MOE_TILE_ROWS = 64                 # rows of a tile of the sorted form
-    MOE_FEW_TOKENS = 32                # up to this many tokens a warp per output number streams the weight rows
+    MOE_TILE_ROWS = 64                 # rows of a tile of the sorted form on CUDA cores
+    MOE_TC_TILE_ROWS = 128             # ... and on the tensor cores (the rows of one MMA)
+    MOE_FEW_TOKENS = 32                # up to this many tokens a warp per output number streams the weight rows (CUDA-core forms)
+    MOE_TC_FEW_TOKENS = 4              # ... where the tensor-core tiles run: beyond it every expert's weights are read once per step
+    _EPI_GLU_CLAMP = 8
 
     def moe_route(self, logits, correction, top, scale, idx, weights):
         T = logits.shape[0]
@@ -523,6 +526,30 @@ class CudaKernels:
         _need(x, torch.float32, (T, D), "residual stream")
         dt = c_int(_dt(h))
         sizes = (c_int(T), c_int(top), c_int(E), c_int(F), c_int(D))
+        if h.dtype == torch.bfloat16 and T > self.MOE_TC_FEW_TOKENS and D % 8 == 0 and F % 8 == 0 and E * max(2 * F, D) < 2 ** 31:
+            # sorted by expert in tiles of 128 rows, both products on the tensor cores: gather the rows, gate/up with the
+            # activation in the epilogue, down into 32-bit rows, then the weighted sum into the stream in pair order
+            rows, pairs = self.MOE_TC_TILE_ROWS, T * top
+            tiles = (pairs + min(E, pairs) * (rows - 1)) // rows
+            plan = torch.empty(tiles * rows + pairs + tiles, dtype=torch.int32, device=h.device)
+            row_pair, pair_row, tile_expert = plan[:tiles * rows], plan[tiles * rows:tiles * rows + pairs], plan[tiles * rows + pairs:]
+            self._call("moe", "gfb_moe_plan", _ptr(idx), c_int(pairs), c_int(E), c_int(rows), _ptr(row_pair), _ptr(pair_row),
+                       _ptr(tile_expert), c_int(tiles), _stream())
+            hs = torch.empty(tiles * rows, D, dtype=h.dtype, device=h.device)
+            self._call("moe", "gfb_moe_gather_rows", _ptr(h), _ptr(row_pair), _ptr(hs), c_int(tiles * rows), c_int(top), c_int(D), _stream())
+            act = torch.empty(tiles * rows, F, dtype=h.dtype, device=h.device)
+            self._label = f"moe_glu_tc {2 * F}x{D}"
+            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(hs), _ptr(w13), _ptr(act), c_int(_dt(act)), c_int(tiles * rows), c_int(E),
+                       c_int(2 * F), c_int(D), c_int(self._EPI_GLU_CLAMP), _ptr(tile_expert), c_float(limit), c_float(alpha),
+                       c_float(shift), _ptr(self.status), _stream())
+            y = torch.empty(tiles * rows, D, dtype=torch.float32, device=h.device)
+            self._label = f"moe_down_tc {D}x{F}"
+            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(act), _ptr(w2), _ptr(y), c_int(_dt(y)), c_int(tiles * rows), c_int(E),
+                       c_int(D), c_int(F), c_int(_EPI["store"]), _ptr(tile_expert), c_float(0.0), c_float(0.0), c_float(0.0),
+                       _ptr(self.status), _stream())
+            self._call("moe", "gfb_moe_combine_rows", _ptr(y), _ptr(pair_row), _ptr(weights), _ptr(x), c_int(T), c_int(top), c_int(D),
+                       _stream())
+            return
         if T <= self.MOE_FEW_TOKENS:
             act = torch.empty(T * top, F, dtype=h.dtype, device=h.device)
             self._call("moe", "gfb_moe_glu", _ptr(h), _ptr(idx), _ptr(w13), _ptr(act), dt, *sizes, c_float(limit), c_float(alpha),

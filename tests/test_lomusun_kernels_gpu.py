@@ -133,3 +133,35 @@ def test_one_strong_key_at_the_edge_of_table_and_window(force, gap):
         torch.testing.assert_close(out, target.expand(H, d), rtol=2e-2, atol=2e-2)
     else:
         assert (out - target).abs().max() > 0.3
+
+
+# ---- the experts' products on the tensor cores ------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("T,E,top,F,D,limit", [(300, 6, 2, 136, 320, 1.5), (5, 3, 3, 8, 8, 0.0), (130, 2, 1, 264, 72, 0.7), (64, 16, 4, 64, 256, 2.0)],
+                         ids=["several-tiles-each-way", "smallest", "one-expert-two-row-tiles", "a-decode-batch"])
+def test_experts_on_the_tensor_cores(T, E, top, F, D, limit):
+    """Rows sorted by expert in tiles of 128, the gate/up product with the clamped activation in its epilogue, the down
+    product and the weighted sum, against the same sums in 64-bit; some experts get no token at all."""
+    g = torch.Generator().manual_seed(T + E)
+    bf = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
+    h, gate, up, down = bf(T, D), bf(E, F, D, s=D ** -0.5), bf(E, F, D, s=D ** -0.5), bf(E, D, F, s=F ** -0.5)
+    busy = max(top, E - 2)                                    # the last experts stay idle
+    idx = torch.stack([torch.randperm(busy, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, top, generator=g) + 0.1
+    alpha, shift = 1.702, 1.0
+    want = torch.zeros(T, D, dtype=torch.float64)
+    for t in range(T):
+        for r in range(top):
+            e = int(idx[t, r])
+            a, b = gate[e].double() @ h[t].double(), up[e].double() @ h[t].double()
+            if limit > 0:
+                a, b = a.clamp(max=limit), b.clamp(-limit, limit)
+            act = (a * torch.sigmoid(alpha * a) * (b + shift)).to(torch.bfloat16).double()
+            want[t] += float(w[t, r]) * (down[e].double() @ act)
+    w13 = torch.stack([gate, up], dim=2).reshape(E, 2 * F, D).contiguous().cuda()
+    x = torch.full((T, D), 0.25, dtype=torch.float32, device="cuda")
+    assert T > ops.kernels().MOE_TC_FEW_TOKENS
+    ops.moe_experts(h.cuda(), idx.cuda(), w.cuda(), w13, down.cuda(), x, limit, alpha, shift)
+    ops.check_status(ops.kernels().status)
+    err = (x.cpu().double() - 0.25 - want).abs().max() / want.abs().max()
+    assert float(err) < 6e-3, float(err)                      # one bfloat16 rounding of the activation, 32-bit sums
