@@ -37,6 +37,7 @@ struct Groups {
     const int* tile_group;
     int group_rows;
     float limit, alpha, shift;
+    const int* tiles_used;      // the pair kernel: how many leading entries of tile_group have rows (the rest is negative)
 };
 
 // what a storing epilogue does to an accumulator value before it rounds it
@@ -236,6 +237,12 @@ __device__ __forceinline__ float glu_clamp(float g, float u, const Groups& gp) {
     return g * (1.0f / (1.0f + expf(-gp.alpha * g))) * (u + gp.shift);
 }
 
+// the gated activation of an epilogue: SiLU(g) u, or the clamped form with the product's constants
+template <int EPI>
+__device__ __forceinline__ float gated(const Groups& gp, float g, float u) {
+    return EPI == EPI_GLU_CLAMP ? glu_clamp(g, u, gp) : silu_mul(g, u);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -323,7 +330,7 @@ __device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int 
 #pragma unroll
             for (int ps = 0; ps < PASSES; ps++) {
                 int c = ps * 128 + lane * 4;
-                if (col0 + c < N)
+                if (c < BN && col0 + c < N)
                     *reinterpret_cast<float4*>((float*)out + (size_t)(row0 + q * 32 + rr) * ldo + col0 + c) =
                         *reinterpret_cast<const float4*>(stage + (size_t)(q * 32 + rr) * SP + c);
             }
@@ -351,7 +358,7 @@ __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                TO* __restrict__ out, float* __restrict__ partial, int R, int Cc, int K, int ldo,
                int kb_per_split, int stages, int* status, const Groups gp) {
-    static_assert(!(GROUPED && SWAP), "groups of row tiles exist in the normal orientation only");
+    constexpr bool GATED = EPI == EPI_SWIGLU || EPI == EPI_GLU_CLAMP;
     constexpr int Y_TILE_BYTES = BN * BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ uint8_t smem_raw[];
@@ -409,10 +416,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     int group = 0;
     if constexpr (GROUPED) {
         if (warp == 0 && lane == 0) gfb_pdl_wait();
-        group = gp.tile_group[blockIdx.x];
+        group = gp.tile_group[SWAP ? blockIdx.y : blockIdx.x];     // the tile of tokens
     }
     const bool idle = GROUPED && group < 0;
-    const int ycol0 = GROUPED ? group * gp.group_rows + col0 : col0;
+    const int xrow0 = GROUPED && SWAP ? group * gp.group_rows + row0 : row0;      // where the weights' rows start
+    const int ycol0 = GROUPED && !SWAP ? group * gp.group_rows + col0 : col0;
 
     if (idle) {
     } else if (warp == 0) {
@@ -424,9 +432,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 uint32_t full = smem_u32(&bars->full[i]);
                 if (GROUPED) {
                     mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                    if (SWAP) tma_load_2d_hint(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, xrow0, full, pol);
+                    else tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, xrow0, full);
                     tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, ycol0, full);
-                }
-                if (SWAP) tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
+                } else if (SWAP) tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
                 else tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
             }
             for (int i = n_pre; i < nkb; i++) {
@@ -435,8 +444,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
                 uint32_t full = smem_u32(&bars->full[s]);
                 mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-                if (SWAP) tma_load_2d_hint(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full, pol);
-                else tma_load_2d(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+                if (SWAP) tma_load_2d_hint(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, xrow0, full, pol);
+                else tma_load_2d(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, xrow0, full);
                 tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, ycol0, full);
             }
         }
@@ -477,7 +486,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // row, so its direct stores are 4 bytes each, 128 per warp and token, and 64 of them per thread kept a
             // block for 3 us; from the staged tile a warp writes a token's 128 rows with one 16-byte store per lane.
             const int ldv = EPI == EPI_PARTIAL ? R : ldo;
-            const bool staged = BN >= 32 && R % 4 == 0 && ldv % (EPI == EPI_SWIGLU ? 2 : 4) == 0;   // uniform over the grid
+            const bool staged = BN >= 32 && R % 4 == 0 && ldv % (GATED ? 2 : 4) == 0;   // uniform over the grid
             if (staged) {
                 float* tile = reinterpret_cast<float*>(aligned);        // [tokens][128 rows]
                 const bool all_ok = epilogue_warps_all(ok);             // all four warps or none
@@ -499,9 +508,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const float4 v = *reinterpret_cast<const float4*>(tile + j * BM + 4 * lane);
                         const float e[4] = {v.x, v.y, v.z, v.w};
                         if (rr + 3 < R) {
-                            if (EPI == EPI_SWIGLU) {
+                            if (GATED) {
                                 *reinterpret_cast<uint32_t*>((__nv_bfloat16*)out + (size_t)m * ldo + (rr >> 1)) =
-                                    pack_bf16(silu_mul(v.x, v.y), silu_mul(v.z, v.w));
+                                    pack_bf16(gated<EPI>(gp, v.x, v.y), gated<EPI>(gp, v.z, v.w));
                             } else if (EPI == EPI_PARTIAL) {
                                 *reinterpret_cast<float4*>(partial + ((size_t)blockIdx.z * Cc + m) * R + rr) = v;
                             } else if (EPI == EPI_ADD) {
@@ -522,8 +531,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             for (int u = 0; u < 4; u++) {
                                 const int r1 = rr + u;
                                 if (r1 >= R) break;
-                                if (EPI == EPI_SWIGLU) {
-                                    if (!(u & 1)) ((__nv_bfloat16*)out)[(size_t)m * ldo + (r1 >> 1)] = __float2bfloat16_rn(silu_mul(e[u], e[u + 1]));
+                                if (GATED) {
+                                    if (!(u & 1)) ((__nv_bfloat16*)out)[(size_t)m * ldo + (r1 >> 1)] = __float2bfloat16_rn(gated<EPI>(gp, e[u], e[u + 1]));
                                 } else if (EPI == EPI_PARTIAL) partial[((size_t)blockIdx.z * Cc + m) * R + r1] = e[u];
                                 else if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + r1] += e[u];
                                 else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + r1] = e[u];
@@ -538,7 +547,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (col0 + c >= Cc) break;                  // uniform: nothing left in this tile
                 uint32_t raw[GROUP];
                 tmem_ld_group<GROUP>(taddr + c, raw);
-                if (EPI == EPI_SWIGLU) {
+                if (GATED) {
                     // Rows 2i (gate) and 2i + 1 (up) sit in neighbouring lanes; the even lane finishes the even
                     // tokens of the pair and the odd lane the odd ones, so each lane does half of the work.
                     const int p = lane & 1;
@@ -550,7 +559,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const int m = col0 + c + j + p;     // token
                         if (m < Cc && r < R)
                             ((__nv_bfloat16*)out)[(size_t)m * ldo + (r >> 1)] =
-                                __float2bfloat16_rn(p ? silu_mul(theirs, mine) : silu_mul(mine, theirs));
+                                __float2bfloat16_rn(p ? gated<EPI>(gp, theirs, mine) : gated<EPI>(gp, mine, theirs));
                     }
                 } else {
 #pragma unroll
@@ -630,7 +639,8 @@ __device__ __forceinline__ void load_residual_chunk(float4 (&res)[RES_N], int c0
 // values for add-into-residual, unused otherwise)
 template <int EPI, typename TO>
 __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0, int lane, TO* out, int grow0, int gcol0,
-                                            int rows, int N, int ldo, const float4 (&res)[RES_N]) {
+                                            int rows, int N, int ldo, const float4 (&res)[RES_N],
+                                            const Groups& gp = Groups{nullptr, 0, 0.f, 0.f, 0.f, nullptr}) {
     float* mine = stage + lane * PSP;
     constexpr int ALPR = RES_LPR, ARPI = RES_RPI, ANL = RES_N;
     {
@@ -656,7 +666,7 @@ __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0
                 *reinterpret_cast<float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col) = a;
             }
         }
-    } else if (EPI == EPI_SWIGLU) {
+    } else if (EPI == EPI_SWIGLU || EPI == EPI_GLU_CLAMP) {
         // PCW/8 lanes x 8 accumulator columns (4 gate/up pairs -> 4 outputs) cover a row
         constexpr int LPR = PCW / 8, RPI = 32 / LPR;
         const int sub = lane / LPR, col = (lane % LPR) * 8;
@@ -667,8 +677,13 @@ __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0
                 const float* a = stage + r * PSP + col;
                 float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
                 uint2 pk;
-                pk.x = pack_bf16(silu_mul(lo.x, lo.y), silu_mul(lo.z, lo.w));
-                pk.y = pack_bf16(silu_mul(hi.x, hi.y), silu_mul(hi.z, hi.w));
+                if (EPI == EPI_SWIGLU) {
+                    pk.x = pack_bf16(silu_mul(lo.x, lo.y), silu_mul(lo.z, lo.w));
+                    pk.y = pack_bf16(silu_mul(hi.x, hi.y), silu_mul(hi.z, hi.w));
+                } else {
+                    pk.x = pack_bf16(glu_clamp(lo.x, lo.y, gp), glu_clamp(lo.z, lo.w, gp));
+                    pk.y = pack_bf16(glu_clamp(hi.x, hi.y, gp), glu_clamp(hi.z, hi.w, gp));
+                }
                 *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(grow0 + r) * ldo + ((gc + col) >> 1)) = pk;
             }
         }
@@ -887,10 +902,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int EPI, typename TO>
+// GROUPED: row tile i (256 rows) multiplies with the weight rows from gp.tile_group[i] * gp.group_rows on; only the first
+// *gp.tiles_used row tiles exist.  Both are written by the kernel ahead, so nothing is fetched before the wait for it.
+template <int EPI, typename TO, bool GROUPED = false>
 __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                    TO* __restrict__ out, int R, int Cc, int K, int ldo, int stages, int* status) {
+                    TO* __restrict__ out, int R, int Cc, int K, int ldo, int stages, int* status, const Groups gp) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 32) { prefetch_map(&map_x); prefetch_map(&map_y); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -905,10 +922,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
-    const int row_tiles = (R + 255) / 256, col_tiles = (Cc + 255) / 256;
-    const int n_tiles = row_tiles * col_tiles;
+    const int col_tiles = (Cc + 255) / 256;
     const int nkb = (K + BK - 1) / BK;
-    const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
@@ -933,14 +948,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
     gfb_pdl_launch();
-    if (!(warp == 0 && lane == 0)) gfb_pdl_wait();
+    if (GROUPED || !(warp == 0 && lane == 0)) gfb_pdl_wait();
+    int row_tiles = (R + 255) / 256;
+    if (GROUPED) row_tiles = max(0, min(row_tiles, *gp.tiles_used));
+    const int n_tiles = row_tiles * col_tiles;
+    const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
+    // the first weight row of a tile's group
+    auto group_row = [&](int tile) -> int { return GROUPED ? max(gp.tile_group[tile % row_tiles], 0) * gp.group_rows : 0; };
 
     if (warp == 0) {
         if (lane == 0) {
             const int total = my_tiles * nkb;
             // Weights are written by no kernel: the weight halves of the first round of the ring are asked for ahead
             // of the wait for the preceding kernel (fresh barriers: every stage is free), the activations behind it.
-            const int n_pre = min(stages, total);
+            const int n_pre = GROUPED ? 0 : min(stages, total);
             {
                 int kb = 0, tile = pair;
                 for (int it = 0; it < n_pre; it++) {
@@ -950,10 +971,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     if (++kb == nkb) { kb = 0; tile += n_pairs; }
                 }
             }
-            gfb_pdl_wait();
+            if (!GROUPED) gfb_pdl_wait();
             int kb = 0, tile = pair, s = 0;
             uint32_t ph = 0;
-            int row0 = (tile % row_tiles) * 256 + (int)rank * 128, wrow0 = (tile / row_tiles) * 256 + (int)rank * 128;
+            int row0 = 0, wrow0 = 0;
+            if (total > 0) {
+                row0 = (tile % row_tiles) * 256 + (int)rank * 128;
+                wrow0 = group_row(tile) + (tile / row_tiles) * 256 + (int)rank * 128;
+            }
             for (int it = 0; it < total; it++) {
                 const uint32_t full = smem_u32(&bars->full[s]) & PEER_MASK;        // the leader's barrier
                 if (it >= n_pre) {
@@ -966,8 +991,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (++kb == nkb) {
                     kb = 0;
                     tile += n_pairs;
-                    row0 = (tile % row_tiles) * 256 + (int)rank * 128;
-                    wrow0 = (tile / row_tiles) * 256 + (int)rank * 128;
+                    if (it + 1 < total) {
+                        row0 = (tile % row_tiles) * 256 + (int)rank * 128;
+                        wrow0 = group_row(tile) + (tile / row_tiles) * 256 + (int)rank * 128;
+                    }
                 }
             }
         }
@@ -1014,7 +1041,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int c0 = 0; c0 < 256; c0 += PCW) {
                 if (col0 + c0 >= Cc || rows <= 0) break;
                 if (EPI == EPI_ADD) load_residual_chunk(res_next, c0 + PCW, lane, out, row0 + q * 32, col0, c0 + PCW < 256 ? rows : 0, Cc, ldo);
-                drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo, res);
+                drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo, res, gp);
                 if (EPI == EPI_ADD) {
 #pragma unroll
                     for (int u = 0; u < RES_N; u++) res[u] = res_next[u];
@@ -1119,14 +1146,14 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* parti
     }
     dim3 grid((R + BM - 1) / BM, (Cc + BN - 1) / BN, splits);
     cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, partial, R, Cc, K, ldo, kb_per_split, stages, status,
-                               Groups{nullptr, 0, 0.f, 0.f, 0.f});
+                               Groups{nullptr, 0, 0.f, 0.f, 0.f, nullptr});
     return gfb_check(e, "gfb_gemm_tc");
 }
 
-template <int BN, int EPI, typename TO>
+template <int BN, int EPI, typename TO, bool SWAP = false>
 int launch_grouped(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, int Cc, int K, int ldo, int stages, int* status,
                    const Groups& gp, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BN, false, EPI, TO, true>;
+    auto kern = gemm_tc_kernel<BN, SWAP, EPI, TO, true>;
     size_t smem = smem_bytes(BN, stages);
     static size_t configured = 0;
     if (smem > configured) {
@@ -1180,8 +1207,35 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, 
     int pairs = sm_count / 2;
     if (tiles < pairs) pairs = tiles;
     cudaError_t e = gfb_launch_cluster(kern, dim3(2 * pairs), dim3(192), smem, stream, 2u, mx, my, (TO*)out, R, Cc, K, ldo,
-                                       stages, status);
+                                       stages, status, Groups{nullptr, 0, 0.f, 0.f, 0.f, nullptr});
     return gfb_check(e, "gfb_gemm_tc (pair)");
+}
+
+template <int EPI, typename TO>
+int launch_pair_grouped(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, int Cc, int K, int ldo, int* status,
+                        const Groups& gp, cudaStream_t stream) {
+    auto kern = gemm_tc_pair_kernel<EPI, TO, true>;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    int stages = MAX_STAGES;
+    while (stages > 2 && pair_smem_bytes(stages) > 227 * 1024) stages--;
+    size_t smem = pair_smem_bytes(stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("gfb_gemm_tc_grouped: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    int tiles = ((R + 255) / 256) * ((Cc + 255) / 256);
+    int pairs = sm_count / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaError_t e = gfb_launch_cluster(kern, dim3(2 * pairs), dim3(192), smem, stream, 2u, mx, my, (TO*)out, R, Cc, K, ldo,
+                                       stages, status, gp);
+    return gfb_check(e, "gfb_gemm_tc_grouped (pair)");
 }
 
 template <int BN, bool SWAP>
@@ -1305,26 +1359,62 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     return 0;
 }
 
-// Row tiles of 128 rows that each use one of `groups` weight matrices: out[r] = A[r] * W[tile_group[r / 128]]^T for
-// A [rows, K] (rows a multiple of 128), W [groups, N, K]; a tile whose entry is negative is skipped.  epi: EPI_STORE
-// with out float32 [rows, N], or EPI_GLU_CLAMP with out bfloat16 [rows, N / 2] from alternating gate/up rows of W.
-GFB_API int gfb_gemm_tc_grouped(const void* A, const void* W, void* out, int out_dt, int rows, int groups, int N, int K, int epi,
-                                const int* tile_group, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
+// Row tiles that each use one of `groups` weight matrices: out[r] = A[r] * W[tile_group[r / tile_rows]]^T for A [rows, K]
+// (rows a multiple of tile_rows), W [groups, N, K].  tile_rows 16, 32, 64: the swapped orientation of a decode step (128 weight
+// rows x a tile of tokens per block); 128: 128 tokens x 128 or 64 weight rows per block; in both a tile whose entry is negative is
+// skipped.  tile_rows 256: pairs of SMs walk over the first *tiles_used row tiles (the entries with rows come first).
+// epi: EPI_STORE with out float32 [rows, N], or EPI_GLU_CLAMP with out bfloat16 [rows, N / 2] from alternating gate/up
+// rows of W.
+GFB_API int gfb_gemm_tc_grouped(const void* A, const void* W, void* out, int out_dt, int rows, int tile_rows, int groups, int N, int K,
+                                int epi, const int* tile_group, const int* tiles_used, float limit, float alpha, float shift,
+                                int* status, cudaStream_t stream) {
     if (rows <= 0 || N <= 0 || groups <= 0) return 0;
-    if (rows % BM) return gfb_fail("gfb_gemm_tc_grouped: %d rows are not whole tiles of %d", rows, BM);
+    if ((tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128 && tile_rows != 256) || rows % tile_rows)
+        return gfb_fail("gfb_gemm_tc_grouped: %d rows in tiles of %d (16 to 256 rows, whole tiles)", rows, tile_rows);
+    if (tile_rows == 256 && tiles_used == nullptr) return gfb_fail("gfb_gemm_tc_grouped: tiles of 256 rows need the count of tiles with rows");
     if (K <= 0 || K % 8) return gfb_fail("gfb_gemm_tc_grouped: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (N % 8) return gfb_fail("gfb_gemm_tc_grouped: N = %d must be a multiple of 8", N);
     if (epi == EPI_GLU_CLAMP && N % 16) return gfb_fail("gfb_gemm_tc_grouped: the gated epilogue needs N %% 16 == 0, got %d", N);
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc_grouped: operands must be 16-byte aligned");
     if ((long)groups * N > 0x7fffffffL) return gfb_fail("gfb_gemm_tc_grouped: %d matrices of %d rows exceed a tensor map's coordinates", groups, N);
-    constexpr int GBN = 128, STAGES = 6;
+    const Groups gp{tile_group, N, limit, alpha, shift, tiles_used};
     CUtensorMap mx, my;
+    if (tile_rows < 128) {
+        // few tokens per group: the weights' rows are the rows of the MMA, a tile of tokens its columns
+        constexpr int STAGES = 8;
+        if (make_map(&mx, W, groups * N, K, BM)) return 1;
+        if (make_map(&my, A, rows, K, tile_rows)) return 1;
+        const bool glu = epi == EPI_GLU_CLAMP && out_dt == GFB_BF16, store = epi == EPI_STORE && out_dt == GFB_F32;
+        const int ldo = glu ? N / 2 : N;
+#define GS(B) return glu ? launch_grouped<B, EPI_GLU_CLAMP, __nv_bfloat16, true>(mx, my, out, N, rows, K, ldo, STAGES, status, gp, stream) \
+                         : launch_grouped<B, EPI_STORE, float, true>(mx, my, out, N, rows, K, ldo, STAGES, status, gp, stream)
+        if (glu || store) {
+            if (tile_rows == 16) GS(16);
+            if (tile_rows == 32) GS(32);
+            GS(64);
+        }
+#undef GS
+        return gfb_fail("gfb_gemm_tc_grouped: unsupported epilogue %d / output type %d", epi, out_dt);
+    }
     if (make_map(&mx, A, rows, K, BM)) return 1;
-    if (make_map(&my, W, groups * N, K, GBN)) return 1;
-    const Groups gp{tile_group, N, limit, alpha, shift};
+    if (tile_rows == 256) {
+        if (make_map(&my, W, groups * N, K, 128)) return 1;
+        if (epi == EPI_GLU_CLAMP && out_dt == GFB_BF16)
+            return launch_pair_grouped<EPI_GLU_CLAMP, __nv_bfloat16>(mx, my, out, rows, N, K, N / 2, status, gp, stream);
+        if (epi == EPI_STORE && out_dt == GFB_F32)
+            return launch_pair_grouped<EPI_STORE, float>(mx, my, out, rows, N, K, N, status, gp, stream);
+        return gfb_fail("gfb_gemm_tc_grouped: unsupported epilogue %d / output type %d", epi, out_dt);
+    }
+    // Few row tiles (a decode step) are bound by the stream of weights: tiles of 64 columns then give twice the blocks,
+    // each with its own ring of copies in flight.
+    constexpr int STAGES = 6;
+    const bool narrow = (long)(rows / BM) * ((N + 127) / 128) < 2 * 148;
+    if (make_map(&my, W, groups * N, K, narrow ? 64 : 128)) return 1;
     if (epi == EPI_GLU_CLAMP && out_dt == GFB_BF16)
-        return launch_grouped<GBN, EPI_GLU_CLAMP, __nv_bfloat16>(mx, my, out, rows, N, K, N / 2, STAGES, status, gp, stream);
+        return narrow ? launch_grouped<64, EPI_GLU_CLAMP, __nv_bfloat16>(mx, my, out, rows, N, K, N / 2, STAGES, status, gp, stream)
+                      : launch_grouped<128, EPI_GLU_CLAMP, __nv_bfloat16>(mx, my, out, rows, N, K, N / 2, STAGES, status, gp, stream);
     if (epi == EPI_STORE && out_dt == GFB_F32)
-        return launch_grouped<GBN, EPI_STORE, float>(mx, my, out, rows, N, K, N, STAGES, status, gp, stream);
+        return narrow ? launch_grouped<64, EPI_STORE, float>(mx, my, out, rows, N, K, N, STAGES, status, gp, stream)
+                      : launch_grouped<128, EPI_STORE, float>(mx, my, out, rows, N, K, N, STAGES, status, gp, stream);
     return gfb_fail("gfb_gemm_tc_grouped: unsupported epilogue %d / output type %d", epi, out_dt);
 }

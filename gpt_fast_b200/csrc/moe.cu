@@ -180,13 +180,14 @@ static int allow_smem(K kernel, size_t smem, const char* what) {
 // ------------------------------------------------------------------------------------ many tokens ----
 // The plan: rows of the sorted order.  Expert e's pairs take rows start[e] .. start[e] + count[e] - 1, start[e] a
 // multiple of the tile height BM; row_pair[row] is the pair of a row (-1: padding), tile_expert[tile] the expert whose
-// weights a tile of that many rows uses (-1: the tile is beyond the last expert's rows).  One block builds it; the order of an
+// weights a tile of that many rows uses (-1: the tile is beyond the last expert's rows), *tiles_used (if asked for) the number
+// of tiles with an expert, which come first.  One block builds it; the order of an
 // expert's rows among themselves is whatever the atomics give, and no result depends on it.
 constexpr int PLAN_THREADS = 1024;
 
 __global__ void __launch_bounds__(PLAN_THREADS)
 moe_plan_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, int* __restrict__ row_pair, int* __restrict__ pair_row,
-                int* __restrict__ tile_expert, int max_tiles) {
+                int* __restrict__ tile_expert, int max_tiles, int* __restrict__ tiles_used) {
     extern __shared__ int sh[];          // count[E], start[E], fill[E]
     int* count = sh;
     int* start = sh + E;
@@ -210,6 +211,7 @@ moe_plan_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, 
             for (int i = 0; i < tiles; i++) tile_expert[at / tile_rows + i] = e;
             at += tiles * tile_rows;
         }
+        if (tiles_used != nullptr) *tiles_used = at / tile_rows;       // the tiles with rows come first
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
@@ -225,14 +227,14 @@ moe_plan_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, 
 }
 
 GFB_API int gfb_moe_plan(const int* idx, int n_pairs, int E, int tile_rows, int* row_pair, int* pair_row, int* tile_expert, int max_tiles,
-                         cudaStream_t stream) {
+                         int* tiles_used, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     const long busy = n_pairs < E ? n_pairs : E;             // experts that can have rows at all
     if (tile_rows < 1 || (long)max_tiles < ((long)n_pairs + busy * (tile_rows - 1)) / tile_rows)
         return gfb_fail("gfb_moe_plan: %d tiles of %d rows cannot hold %d pairs of %d experts", max_tiles, tile_rows, n_pairs, E);
     const size_t smem = (size_t)3 * E * sizeof(int);
     cudaError_t e = gfb_launch(moe_plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, stream, idx, n_pairs, E, tile_rows, row_pair, pair_row,
-                               tile_expert, max_tiles);
+                               tile_expert, max_tiles, tiles_used);
     return gfb_check(e, "gfb_moe_plan");
 }
 

@@ -499,7 +499,8 @@ class CudaKernels:
     MOE_TILE_ROWS = 64                 # rows of a tile of the sorted form on CUDA cores
     MOE_TC_TILE_ROWS = 128             # ... and on the tensor cores (the rows of one MMA)
     MOE_FEW_TOKENS = 32                # up to this many tokens a warp per output number streams the weight rows (CUDA-core forms)
-    MOE_TC_FEW_TOKENS = 4              # ... where the tensor-core tiles run: beyond it every expert's weights are read once per step
+    MOE_TC_FEW_TOKENS = 0              # ... where the tensor-core tiles run: they stream a chosen expert's weights once per step by TMA
+    MOE_PAIR_ROWS_PER_EXPERT = 384     # (token, expert) pairs per expert from which the row tiles have 256 rows
     _EPI_GLU_CLAMP = 8
 
     def moe_route(self, logits, correction, top, scale, idx, weights):
@@ -529,23 +530,29 @@ class CudaKernels:
         if h.dtype == torch.bfloat16 and T > self.MOE_TC_FEW_TOKENS and D % 8 == 0 and F % 8 == 0 and E * max(2 * F, D) < 2 ** 31:
             # sorted by expert in tiles of 128 rows, both products on the tensor cores: gather the rows, gate/up with the
             # activation in the epilogue, down into 32-bit rows, then the weighted sum into the stream in pair order
-            rows, pairs = self.MOE_TC_TILE_ROWS, T * top
+            pairs = T * top
+            # from about two full tiles per expert on: tiles of 256 rows for pairs of SMs (tcgen05 cta_group::2)
+            # a decode step: an expert has at most T rows, so tiles of at least T rows (the columns of the swapped MMA) read
+            # every chosen expert's weights exactly once
+            rows = (16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else
+                    self.MOE_TC_TILE_ROWS * (2 if pairs >= self.MOE_PAIR_ROWS_PER_EXPERT * E else 1))
             tiles = (pairs + min(E, pairs) * (rows - 1)) // rows
-            plan = torch.empty(tiles * rows + pairs + tiles, dtype=torch.int32, device=h.device)
-            row_pair, pair_row, tile_expert = plan[:tiles * rows], plan[tiles * rows:tiles * rows + pairs], plan[tiles * rows + pairs:]
+            plan = torch.empty(tiles * rows + pairs + tiles + 1, dtype=torch.int32, device=h.device)
+            row_pair, pair_row = plan[:tiles * rows], plan[tiles * rows:tiles * rows + pairs]
+            tile_expert, tiles_used = plan[tiles * rows + pairs:-1], plan[-1:]
             self._call("moe", "gfb_moe_plan", _ptr(idx), c_int(pairs), c_int(E), c_int(rows), _ptr(row_pair), _ptr(pair_row),
-                       _ptr(tile_expert), c_int(tiles), _stream())
+                       _ptr(tile_expert), c_int(tiles), _ptr(tiles_used), _stream())
             hs = torch.empty(tiles * rows, D, dtype=h.dtype, device=h.device)
             self._call("moe", "gfb_moe_gather_rows", _ptr(h), _ptr(row_pair), _ptr(hs), c_int(tiles * rows), c_int(top), c_int(D), _stream())
             act = torch.empty(tiles * rows, F, dtype=h.dtype, device=h.device)
             self._label = f"moe_glu_tc {2 * F}x{D}"
-            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(hs), _ptr(w13), _ptr(act), c_int(_dt(act)), c_int(tiles * rows), c_int(E),
-                       c_int(2 * F), c_int(D), c_int(self._EPI_GLU_CLAMP), _ptr(tile_expert), c_float(limit), c_float(alpha),
+            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(hs), _ptr(w13), _ptr(act), c_int(_dt(act)), c_int(tiles * rows), c_int(rows), c_int(E),
+                       c_int(2 * F), c_int(D), c_int(self._EPI_GLU_CLAMP), _ptr(tile_expert), _ptr(tiles_used), c_float(limit), c_float(alpha),
                        c_float(shift), _ptr(self.status), _stream())
             y = torch.empty(tiles * rows, D, dtype=torch.float32, device=h.device)
             self._label = f"moe_down_tc {D}x{F}"
-            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(act), _ptr(w2), _ptr(y), c_int(_dt(y)), c_int(tiles * rows), c_int(E),
-                       c_int(D), c_int(F), c_int(_EPI["store"]), _ptr(tile_expert), c_float(0.0), c_float(0.0), c_float(0.0),
+            self._call("gemm_tc", "gfb_gemm_tc_grouped", _ptr(act), _ptr(w2), _ptr(y), c_int(_dt(y)), c_int(tiles * rows), c_int(rows), c_int(E),
+                       c_int(D), c_int(F), c_int(_EPI["store"]), _ptr(tile_expert), _ptr(tiles_used), c_float(0.0), c_float(0.0), c_float(0.0),
                        _ptr(self.status), _stream())
             self._call("moe", "gfb_moe_combine_rows", _ptr(y), _ptr(pair_row), _ptr(weights), _ptr(x), c_int(T), c_int(top), c_int(D),
                        _stream())
@@ -564,7 +571,7 @@ class CudaKernels:
         plan = torch.empty(tiles * rows + pairs + tiles, dtype=torch.int32, device=h.device)
         row_pair, pair_row, tile_expert = plan[:tiles * rows], plan[tiles * rows:tiles * rows + pairs], plan[tiles * rows + pairs:]
         self._call("moe", "gfb_moe_plan", _ptr(idx), c_int(pairs), c_int(E), c_int(rows), _ptr(row_pair), _ptr(pair_row),
-                   _ptr(tile_expert), c_int(tiles), _stream())
+                   _ptr(tile_expert), c_int(tiles), _ptr(None), _stream())
         act = torch.empty(tiles * rows, F, dtype=h.dtype, device=h.device)
         y = torch.empty(pairs, D, dtype=torch.float32, device=h.device)
         self._call("moe", "gfb_moe_glu", _ptr(h), _ptr(idx), _ptr(w13), _ptr(act), dt, *sizes, c_float(limit), c_float(alpha),

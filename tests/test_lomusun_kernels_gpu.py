@@ -137,10 +137,14 @@ def test_one_strong_key_at_the_edge_of_table_and_window(force, gap):
 
 # ---- the experts' products on the tensor cores ------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("T,E,top,F,D,limit", [(300, 6, 2, 136, 320, 1.5), (5, 3, 3, 8, 8, 0.0), (130, 2, 1, 264, 72, 0.7), (64, 16, 4, 64, 256, 2.0)],
-                         ids=["several-tiles-each-way", "smallest", "one-expert-two-row-tiles", "a-decode-batch"])
+@pytest.mark.parametrize("T,E,top,F,D,limit", [(300, 6, 2, 136, 320, 1.5), (5, 3, 3, 8, 8, 0.0), (130, 2, 1, 264, 72, 0.7), (64, 16, 4, 72, 192, 1.2),
+                                                   (1, 4, 2, 200, 328, 1.0), (900, 2, 1, 136, 320, 1.5), (1300, 3, 1, 40, 264, 0.0),
+                                                   (700, 4, 3, 264, 72, 0.9), (20, 5, 2, 24, 40, 0.8)],
+                         ids=["several-tiles-each-way", "smallest", "one-expert-two-row-tiles", "a-decode-batch", "one-token",
+                              "tiles-of-256-rows", "tiles-of-256-rows-all-of-one-expert", "tiles-of-256-rows-three-each", "tiles-of-32-tokens"])
 def test_experts_on_the_tensor_cores(T, E, top, F, D, limit):
-    """Rows sorted by expert in tiles of 128, the gate/up product with the clamped activation in its epilogue, the down
+    """Rows sorted by expert in tiles (16 to 64 tokens as the columns of the swapped MMA in a decode step, 128 rows, 256 rows for
+    pairs of SMs from about two full tiles per expert on), the gate/up product with the clamped activation in its epilogue, the down
     product and the weighted sum, against the same sums in 64-bit; some experts get no token at all."""
     g = torch.Generator().manual_seed(T + E)
     bf = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
