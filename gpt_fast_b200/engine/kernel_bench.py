@@ -7,6 +7,7 @@ the small, self-ending workload that profiler captures are taken on.
     python -m gpt_fast_b200.engine.kernel_bench attention --batch 8 --context 4000
     python -m gpt_fast_b200.engine.kernel_bench attention --batch 1 --context 0 --new 2048
     python -m gpt_fast_b200.engine.kernel_bench sample --batch 8 --vocab 128256
+    python -m gpt_fast_b200.engine.kernel_bench experts --tokens 2048 --experts 16 --top 4 --ff 1792 --dim 2048
 
 Weights are cycled through enough copies to exceed the L2 cache, so a memory-
 bound kernel is timed against DRAM.  gpt-fast has no per-kernel timing; its
@@ -126,6 +127,34 @@ def bench_norm(a):
     print(f"rmsnorm rows={a.rows} dim={a.dim} pending partial sums={a.partials}: {us:.1f} us")
 
 
+def bench_experts(a):
+    """The experts of a mixture (sort by expert, gather, gate/up with the activation, down, weighted sum), every kernel
+    timed by events of its own (the weights of all experts exceed the L2 cache at the default sizes)."""
+    T, E, top, F, D = a.tokens, a.experts, a.top, a.ff, a.dim
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w13 = (torch.randn(E, 2 * F, D, device="cuda", generator=g) * D ** -0.5).bfloat16()
+    w2 = (torch.randn(E, D, F, device="cuda", generator=g) * F ** -0.5).bfloat16()
+    h = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda", generator=g)[:top] for _ in range(T)]).int()
+    w = torch.rand(T, top, device="cuda", generator=g)
+    x = torch.zeros(T, D, device="cuda")
+    flush = torch.empty(int(2 * L2_BYTES), dtype=torch.uint8, device="cuda")
+    best = {}
+    for i in range(a.reps + 2):
+        flush.zero_()
+        torch.cuda.synchronize()
+        with ops.trace() as rec:
+            ops.moe_experts(h, idx, w, w13, w2, x, a.limit, 1.702, 1.0)
+        for label, ms in ops.trace_times(rec):
+            if i >= 2:
+                label = label.split(" ")[0]
+                best[label] = min(best.get(label, 1e9), ms * 1e3)
+    total = sum(best.values())
+    busy = len(torch.unique(idx))
+    print(f"experts T={T} E={E} top={top} ff={F} dim={D}: " + ", ".join(f"{k} {v:.1f}" for k, v in best.items()) + f" us; total {total:.1f} us, "
+          f"{2.0 * T * top * 3 * F * D / total / 1e6:.0f} TFLOP/s, the {busy} chosen experts' weights at {busy * 3 * F * D * 2 / total / 1e3:.0f} GB/s")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kernel_bench")
     sub = ap.add_subparsers(dest="what", required=True)
@@ -148,8 +177,13 @@ def main(argv=None):
     p = sub.add_parser("norm")
     p.add_argument("--rows", type=int, default=8); p.add_argument("--dim", type=int, default=4096)
     p.add_argument("--partials", type=int, default=9); p.add_argument("--reps", type=int, default=10)
+    p = sub.add_parser("experts")
+    p.add_argument("--tokens", type=int, default=2048); p.add_argument("--experts", type=int, default=16)
+    p.add_argument("--top", type=int, default=4); p.add_argument("--ff", type=int, default=1792)
+    p.add_argument("--dim", type=int, default=2048); p.add_argument("--limit", type=float, default=7.0)
+    p.add_argument("--reps", type=int, default=5)
     a = ap.parse_args(argv)
-    {"linear": bench_linear, "attention": bench_attention, "sample": bench_sample, "norm": bench_norm}[a.what](a)
+    {"experts": bench_experts, "linear": bench_linear, "attention": bench_attention, "sample": bench_sample, "norm": bench_norm}[a.what](a)
     ops.check_status(ops.new_status("cuda"))
     return 0
 
