@@ -531,7 +531,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = mbar_wait(smem_u32(&bars->s_full[sb]), (jj >> 1) & 1u, abort_flag, status, 8);
                 if (!ok) break;
                 tc_fence_after();
-                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.last_lo || window > 0 || t.nq < TQ;
+                // a block needs no mask when the tile's first row sees its last key and its last row (whose window or chunk
+                // starts latest) sees its first key
+                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.last_lo || t.nq < TQ;
                 // this warp's half of the row into registers
                 uint32_t raw[2][32];
                 tmem_ld32_issue(lane_base + COL_S + sb * 128 + half * 64, raw[0]);
@@ -901,7 +903,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             ok = mbar_wait(smem_u32(&bars->s_full[x]), n_done & 1u, abort_flag, status, 8);
             if (!ok) break;
             tc_fence_after();
-            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < last_lo || window > 0 || nq[x] < TQ;
+            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < last_lo || nq[x] < TQ;
             float v[4][32];
             tmem_ld_row128(lane_base + col_s, v);
             if (db.table != nullptr || db.slopes != nullptr)
