@@ -1381,7 +1381,9 @@ GFB_API int gfb_gemm_tc_grouped(const void* A, const void* W, void* out, int out
     CUtensorMap mx, my;
     if (tile_rows < 128) {
         // few tokens per group: the weights' rows are the rows of the MMA, a tile of tokens its columns
-        constexpr int STAGES = 8;
+        // rings short enough for two blocks per SM: one block's set-up and epilogue hide behind the other's stream of weights
+        int STAGES = (100 * 1024) / (X_TILE_BYTES + tile_rows * BK * 2);
+        STAGES = STAGES < 2 ? 2 : STAGES > 8 ? 8 : STAGES;
         if (make_map(&mx, W, groups * N, K, BM)) return 1;
         if (make_map(&my, A, rows, K, tile_rows)) return 1;
         const bool glu = epi == EPI_GLU_CLAMP && out_dt == GFB_BF16, store = epi == EPI_STORE && out_dt == GFB_F32;
