@@ -55,6 +55,7 @@ struct Bars {
     unsigned long long o_full;                // the item's last P V has landed (one phase per item)
     unsigned long long xch[4];                // per quarter of the rows: both warps of a row have written their half's maximum
     unsigned long long fin[4];                // the same for their sums at the end of an item
+    unsigned long long tbl_free, tbl_full;    // the distance table in shared memory: all eight softmax warps have left the previous item's / written this item's
     uint32_t tmem_base;
     int abort_flag;
     float mx_half[2][2][ROWS];                // [key block parity][half][row]
@@ -265,11 +266,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //           Copy s is the array moved down by s entries, so the 16-byte loads of a thread, whose first entry can have
 //           any index, are aligned in the copy s = index mod 4.
 //   slopes  null, or [H]: slopes[h] * n is taken off.
+//   s_len, s_stride  (the one-tile kernel) not 0: the softmax warps copy the item's heads into shared memory, s_len entries
+//           per head s_stride apart, entry k for distance k - TABLE_AHEAD, and read their biases there: read from global
+//           memory, four copies of every head of a group outgrow the L1 cache and every block waits for L2.
 struct DistanceBias {
     const float* table;
     int len, top;
     const float* slopes;
+    int s_len, s_stride;
 };
+constexpr int TABLE_AHEAD = 256;         // entries for keys behind the query (masked): a tile's last block reaches up to 254 keys past a row
+constexpr int TABLE_BEYOND = 256;        // entries past the window: a tile's first block starts up to 127 keys before its first row's window, rows are up to 127 apart
 
 // v[c][i] belongs to key key0 + 32 c + i.
 template <int NC>
@@ -365,6 +372,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t ks = base + TILE_BYTES;                               // KV_STAGES x same, rows = keys
     const uint32_t vs = ks + KV_STAGES * TILE_BYTES;
     Bars* bars = reinterpret_cast<Bars*>(aligned + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES);
+    float* bias_s = reinterpret_cast<float*>(aligned + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + ((sizeof(Bars) + 15) & ~(size_t)15));
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -399,6 +407,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         for (int s = 0; s < 2; s++) mbar_init(smem_u32(&bars->pv_done[s]), 1);
         mbar_init(smem_u32(&bars->o_full), 1);
+        mbar_init(smem_u32(&bars->tbl_free), 8);
+        mbar_init(smem_u32(&bars->tbl_full), 8);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -524,6 +534,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool row_ok = tq < t.nq;
             const int row_pos = t.pos0 + tq;
             const int row_lo = first_key(row_pos, window, chunk);
+            if (db.s_stride > 0) {
+                // the table of this item's heads: wait until no warp reads the previous item's, write a share, wait for all shares
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->tbl_free));
+                ok = mbar_wait(smem_u32(&bars->tbl_free), it & 1u, abort_flag, status, 15);
+                if (!ok) break;
+                for (int k = (warp - 2) * 32 + lane; k < rep * db.s_len; k += 256) {
+                    const int hl = k / db.s_len, kk = k - hl * db.s_len;
+                    const int u = min(max(db.top - (kk - TABLE_AHEAD), 0), db.len - 1);
+                    bias_s[hl * db.s_stride + kk] = __ldg(db.table + (size_t)(t.g * rep + hl) * db.len + u);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->tbl_full));
+                ok = mbar_wait(smem_u32(&bars->tbl_full), it & 1u, abort_flag, status, 16);
+                if (!ok) break;
+            }
             float m_run = -INFINITY, l_run = 0.f;                        // l_run: this warp's half of the row's sum
             for (int j = 0; j < t.n_iter && ok; j++, jj++) {
                 const uint32_t sb = jj & 1u;
@@ -548,7 +574,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[c][i] = __uint_as_float(raw[c][i]);
-                if (db.table != nullptr || db.slopes != nullptr)
+                if (db.s_stride > 0) {
+                    // ascending keys are descending distances; the strides keep the lanes of a warp on different banks
+                    const float* e = bias_s + (r - tq * rep) * db.s_stride + TABLE_AHEAD + (row_pos - key0);
+#pragma unroll
+                    for (int c = 0; c < 2; c++)
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[c][i] += e[-(c * 32 + i)];
+                    if (db.slopes != nullptr) {
+                        DistanceBias only_slopes = db;
+                        only_slopes.table = nullptr;
+                        add_distance_bias<2>(v, only_slopes, H, t.g * rep + (r - tq * rep), row_pos, key0);
+                    }
+                } else if (db.table != nullptr || db.slopes != nullptr)
                     add_distance_bias<2>(v, db, H, t.g * rep + (r - tq * rep), row_pos, key0);
                 if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
 #pragma unroll
@@ -1069,7 +1107,7 @@ GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, v
                             || (reinterpret_cast<uintptr_t>(bias) & 15)))
         return gfb_fail("gfb_attn_prefill_tc: a distance array of %d entries with distance 0 at %d (128 far entries ahead of the table, "
                         "384 behind distance 0, a multiple of 4, 16-byte aligned)", bias_len, bias_top);
-    const DistanceBias db{bias, bias_len, bias_top, slopes};
+    DistanceBias db{bias, bias_len, bias_top, slopes, 0, 0};
     if (page_size != PAGE || (d != 64 && d != 128))
         return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim 64 or 128, got %d and %d", PAGE, page_size, d);
     if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
@@ -1126,13 +1164,26 @@ GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, v
         e = gfb_launch(attn_prefill_tc2_kernel, grid, dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                        page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, status);
     } else {
-        size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
-        static bool configured = false;
-        if (!configured) {
+        size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + ((sizeof(Bars) + 15) & ~(size_t)15);
+        if (bias != nullptr && window > 0) {
+            // the table of a group's heads in shared memory, where it fits beside the tiles: every distance a tile can meet
+            // under its window, the stride chosen so that the 32 rows of a warp (tokens x heads of the group) read 32 banks
+            const int s_len = TABLE_AHEAD + window + TABLE_BEYOND;
+            const int want = 32 % rep == 0 ? (32 / rep) % 32 : 1;
+            const int s_stride = s_len + ((want - s_len) % 32 + 32) % 32;
+            const size_t bytes = (size_t)rep * s_stride * sizeof(float);
+            if (smem + bytes <= 227 * 1024) {
+                db.s_len = s_len;
+                db.s_stride = s_stride;
+                smem += bytes;
+            }
+        }
+        static size_t configured = 0;
+        if (smem > configured) {
             cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (a == cudaSuccess) a = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
-            configured = true;
+            configured = smem;
         }
         const int n_x = (n_tokens + TQ - 1) / TQ + n_seqs;           // an upper bound of the tiles; surplus items are empty
         long blocks = (long)n_x * G;

@@ -93,18 +93,27 @@ def bench_attention(a):
               f"K/V at {kv_bytes / us / 1e3:.0f} GB/s")
         ops.check_status(meta.status)
         return
+    window = a.window or None
+    extra = {}
+    if a.bias == "table":                                   # a bias by head and distance: one row per distance up to the window
+        extra["bias"] = torch.randn(window or a.context + a.new, H, device="cuda") * 0.5
+    elif a.bias == "slopes":
+        extra["slopes"] = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device="cuda")
     if a.new > 1 and a.tiles:
-        run = lambda i: ops.kernels()._attention_bf16(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), None, prefill=True, tiles=a.tiles,
-                                                      max_blocks=a.max_blocks)
+        run = lambda i: ops.kernels()._attention_bf16(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), window, prefill=True, tiles=a.tiles,
+                                                      max_blocks=a.max_blocks, **extra)
     else:
-        run = lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d))
+        run = lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), window, **extra)
     us = graph_time_us(run, a.reps)
+    what = f"window={a.window} bias={a.bias}"
     if a.new == 1:
-        print(f"attention decode batch={a.batch} context={a.context}: {us:.1f} us, K/V at {kv_bytes / us / 1e3:.0f} GB/s")
+        print(f"attention decode batch={a.batch} context={a.context} {what}: {us:.1f} us, K/V at {kv_bytes / us / 1e3:.0f} GB/s")
     else:
         T0, T1 = a.context, a.context + a.new
-        flops = a.batch * 4.0 * H * d * (T1 * (T1 + 1) / 2 - T0 * (T0 + 1) / 2)
-        print(f"attention prefill batch={a.batch} context={a.context} new={a.new}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+        seen = sum(min(p + 1, window or p + 1) for p in range(T0, T1))      # keys the queries see
+        flops = a.batch * 4.0 * H * d * seen
+        print(f"attention prefill batch={a.batch} context={a.context} new={a.new} {what}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s "
+              f"(of the keys seen)")
     ops.check_status(meta.status)
 
 
@@ -166,6 +175,8 @@ def main(argv=None):
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=4000)
     p.add_argument("--new", type=int, default=1); p.add_argument("--heads", type=int, default=32)
     p.add_argument("--kv_heads", type=int, default=8); p.add_argument("--head_dim", type=int, default=128)
+    p.add_argument("--window", type=int, default=0, help="only the latest so many positions are seen (0: all)")
+    p.add_argument("--bias", default="none", choices=["none", "table", "slopes"], help="a bias on the score by head and distance")
     p.add_argument("--tiles", type=int, default=0, help="prefill, head_dim 128: query tiles per block of the tcgen05 kernel (0: its own choice)")
     p.add_argument("--max_blocks", type=int, default=0, help="with --tiles 1: cap of the persistent kernel's grid (0: one block per SM)")
     p.add_argument("--partials", type=int, default=-1,
