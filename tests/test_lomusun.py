@@ -355,3 +355,58 @@ def test_cli_greedy(folders, tmp_path, dtype):
     assert [len(x["prompt"]) for x in rows] == [4, 13]
     for x in rows:
         assert len(x["tokens"]) == 7
+
+
+# ---- the head sizes and widths at which the tensor-core kernels run, through the whole engine -----------------------------------
+
+def _moe(E, top, ff, limit=1.3, scale=1.4):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": E, "top": top, "scale": scale}}
+
+
+TC_SIZES = {
+    "architecture": "Lomusun", "vocab": 211, "width": 192, "max_positions": 700, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mlp": _moe(6, 2, 48),
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 3, "mask": {"size": 150}, "scale": 0.12, "bias_max": 90, "bias_rows": 20}},
+        {"type": "parallel", "mlp": _moe(12, 5, 40),
+         "mixer": {"left": {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 128, "mask": {"size": 200}, "scale": 0.09},
+                   "right": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 128, "conv": 2}, "left_scale": 0.9, "right_scale": 1.2}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 6, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 4, "mask": {"size": 70}, "scale": 0.1, "bias_max": 200, "bias_rows": 33,
+                   "kv_from": 0}},
+        {"type": "attention", "mlp": _moe(3, 1, 64),
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 2, "mask": {"size": 333}, "scale": 0.08, "bias_max": 300, "bias_rows": 24}},
+    ]}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tensor_core_head_sizes_through_the_engine(tmp_path, dtype):
+    """Heads of 64 and 128 and a width of whole 16-byte rows: in bfloat16 the tcgen05 attention (table in shared memory, slopes and
+    sink, a reader of another layer's keys) and the grouped expert products run, in prompts longer than every window, in
+    portions, in a batch of unequal requests and in decode steps; 32-bit runs the same model on CUDA cores."""
+    folder = str(tmp_path / "tc_sizes")
+    gf.write_model_folder(folder, TC_SIZES, seed=77, std=0.08, jitter=0.2)
+    model, cache, st = make(folder, ("cuda", dtype))
+    toks = tokens_of(TC_SIZES["vocab"], 520, seed=8)
+    (slot,) = cache.begin(1)
+    whole = st.step([slot], [toks], "all")
+    st.check()
+    cache.end([slot])
+    judge(whole, folder, toks, slice(None), dtype, "a prompt longer than every window")
+    (slot,) = cache.begin(1)
+    cut = stepped(st, slot, toks, (130, 132, 389, 390, 391, 392, 393, 394, 395, 396, 397, 398, 399, 400))
+    cache.end([slot])
+    judge(cut, folder, toks, slice(None), dtype, "portions and decode steps")
+    others = [tokens_of(TC_SIZES["vocab"], n, seed=n) for n in (77, 9)]
+    slots = cache.begin(3)
+    got = st.step(slots, [toks[:300], others[0][:71], others[1][:3]], "all")
+    steps = [st.step(slots, [[toks[300 + i]], [others[0][71 + i]], [others[1][3 + i]]], "all") for i in range(6)]   # decoded together
+    st.check()
+    cache.end(slots)
+    judge(got[:300], folder, toks, slice(0, 300), dtype, "the long request of a batch")
+    judge(got[300:371], folder, others[0], slice(0, 71), dtype, "the second request of a batch")
+    decoded = torch.stack(steps)                                 # [step, request, vocab]
+    judge(decoded[:, 0], folder, toks, slice(300, 306), dtype, "the long request decoded in a batch")
+    judge(decoded[:, 1], folder, others[0], slice(71, 77), dtype, "the second request decoded in a batch")
+    judge(decoded[:, 2], folder, others[1], slice(3, 9), dtype, "the short request decoded in a batch")
