@@ -1,5 +1,6 @@
 // Mixture of experts: a router that picks `top` of E small gated feed-forwards per token, and the experts.
 //
+// gfb_moe_router        few tokens: router logits and choice in one launch (a block per token)
 // gfb_moe_route         from 32-bit router logits: s = sigmoid(z); the `top` experts with the largest s + correction
 //                       (lowest index on ties); weights s / (sum of the chosen s + 1e-20) * scale
 // gfb_moe_glu           act[pair, f] = g * sigmoid(alpha g) * (u + shift),  g = min(gate_f . h, limit),
@@ -30,20 +31,15 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 constexpr int MAX_EPL = 16;           // experts per lane: E <= 512
 constexpr int ROUTE_WARPS = 4;
 
-__global__ void __launch_bounds__(32 * ROUTE_WARPS)
-moe_route_kernel(const float* __restrict__ logits, int ld, const void* __restrict__ correction, int c_dt, int E, int top,
-                 float scale, int* __restrict__ idx, float* __restrict__ weights, int T) {
-    gfb_pdl_launch();
-    gfb_pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
-    if (t >= T) return;
+// one token's choice by one warp: `logits` are the token's E router logits
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, const void* __restrict__ correction, int c_dt, int E, int top,
+                                            float scale, int* __restrict__ idx, float* __restrict__ weights, int lane) {
     float s[MAX_EPL], c[MAX_EPL];
 #pragma unroll
     for (int i = 0; i < MAX_EPL; i++) {
         const int e = lane + 32 * i;
         if (e < E) {
-            s[i] = sigmoid_f(logits[(size_t)t * ld + e]);
+            s[i] = sigmoid_f(logits[e]);
             c[i] = s[i] + (correction != nullptr ? ldw(correction, c_dt, e) : 0.f);
         } else {
             s[i] = 0.f;
@@ -71,9 +67,20 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const void* __restric
         if (lane == r) { mine = best_s; mine_e = best_e; }
     }
     if (lane < top) {
-        idx[(size_t)t * top + lane] = mine_e;
-        weights[(size_t)t * top + lane] = mine / (sum + 1e-20f) * scale;
+        idx[lane] = mine_e;
+        weights[lane] = mine / (sum + 1e-20f) * scale;
     }
+}
+
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_kernel(const float* __restrict__ logits, int ld, const void* __restrict__ correction, int c_dt, int E, int top,
+                 float scale, int* __restrict__ idx, float* __restrict__ weights, int T) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
+    if (t >= T) return;
+    route_token(logits + (size_t)t * ld, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane);
 }
 
 GFB_API int gfb_moe_route(const float* logits, int ld, const void* correction, int c_dt, int E, int top, float scale, int* idx,
@@ -112,6 +119,50 @@ __device__ __forceinline__ float row_dot(const T* __restrict__ row, const float*
 template <typename T>
 __device__ __forceinline__ bool rows_wide(const T* base, int n) {
     return n % Vec<T>::N == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+
+// A decode step's router in one launch: a block per token computes the E logits (a warp per expert row, the token's input
+// staged in shared memory in 32-bit) and its first warp chooses.
+constexpr int ROUTER_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * ROUTER_WARPS)
+moe_router_kernel(const T* __restrict__ h, const T* __restrict__ router, const void* __restrict__ correction, int c_dt, int E, int top,
+                  float scale, int* __restrict__ idx, float* __restrict__ weights, int D) {
+    extern __shared__ __align__(16) float rs[];        // the input [D], then the logits [E]
+    float* z = rs + D;
+    gfb_pdl_launch();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x;
+    gfb_pdl_wait();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) rs[i] = gfb_to_f32(h[(size_t)t * D + i]);
+    __syncthreads();
+    const bool wide = rows_wide(router, D);
+    for (int e = warp; e < E; e += ROUTER_WARPS) {
+        const float d = row_dot(router + (size_t)e * D, rs, D, lane, wide);
+        if (lane == 0) z[e] = d;
+    }
+    __syncthreads();
+    if (warp == 0) route_token(z, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane);
+}
+
+// h [T, D] and router [>= E, D] of type dt (rows beyond E are padding); few tokens only: a block per token
+GFB_API int gfb_moe_router(const void* h, const void* router, int dt, const void* correction, int c_dt, int E, int top, float scale,
+                           int* idx, float* weights, int T, int D, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || E > 32 * MAX_EPL) return gfb_fail("gfb_moe_router: %d experts (1 to %d)", E, 32 * MAX_EPL);
+    if (top < 1 || top > 32 || top > E) return gfb_fail("gfb_moe_router: %d of %d experts per token (1 to 32)", top, E);
+    const size_t smem = (size_t)(D + E) * sizeof(float);
+    if (smem > 48 * 1024) return gfb_fail("gfb_moe_router: %zu bytes of shared memory", smem);
+    cudaError_t e;
+    if (dt == GFB_BF16)
+        e = gfb_launch(moe_router_kernel<__nv_bfloat16>, dim3((unsigned)T), dim3(32 * ROUTER_WARPS), smem, stream, (const __nv_bfloat16*)h,
+                       (const __nv_bfloat16*)router, correction, c_dt, E, top, scale, idx, weights, D);
+    else if (dt == GFB_F32)
+        e = gfb_launch(moe_router_kernel<float>, dim3((unsigned)T), dim3(32 * ROUTER_WARPS), smem, stream, (const float*)h, (const float*)router,
+                       correction, c_dt, E, top, scale, idx, weights, D);
+    else return gfb_fail("gfb_moe_router: unknown type %d", dt);
+    return gfb_check(e, "gfb_moe_router");
 }
 
 constexpr int GEMV_WARPS = 8;
@@ -259,7 +310,7 @@ moe_tiles_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     if (threadIdx.x < BM) {
         const int p = row_pair[m0 + threadIdx.x];
-        src_row[threadIdx.x] = p < 0 ? -1 : (GLU ? p / top : m0 + threadIdx.x);
+        src_row[threadIdx.x] = p < 0 ? -1 : (GLU ? p / top : m0 + (int)threadIdx.x);
     }
     __syncthreads();
     const T* We = W + (size_t)e * N * K;

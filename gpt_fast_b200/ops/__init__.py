@@ -248,6 +248,19 @@ def moe_route(logits, correction, top: int, scale: float, idx, weights):
     return kernels().moe_route(logits, correction, top, scale, idx, weights)
 
 
+def moe_router(h, router, correction, top: int, scale: float, idx, weights):
+    """Router logits z = h router^T (32-bit) and `moe_route` on them.  h [T, D]; router [>= E, D] (rows beyond the E of
+    `correction` are padding).  A set of kernels may do both in one launch (`moe_router` returning True); otherwise the
+    product and the choice run one after the other."""
+    k = kernels()
+    fused = getattr(k, "moe_router", None)
+    if fused is not None and fused(h, router, correction, top, scale, idx, weights):
+        return
+    z = torch.empty(h.shape[0], router.shape[0], dtype=torch.float32, device=h.device)
+    linear(h, router, z)
+    moe_route(z, correction, top, scale, idx, weights)
+
+
 def moe_experts(h, idx, weights, w13, w2, x, limit: float, alpha: float, shift: float = 1.0):
     """x float32 [T, D] += sum_r weights[t, r] * W2_e (g * sigmoid(alpha g) * (u + shift)), e = idx[t, r],
     g = min(gate_e h, limit), u = clamp(up_e h, -limit, limit) (limit <= 0: no clamps).  w13 [E, 2F, D]: rows alternate

@@ -515,6 +515,24 @@ class CudaKernels:
         self._call("moe", "gfb_moe_route", _ptr(logits), c_int(logits.shape[1]), _ptr(correction), c_int(_dt(correction)), c_int(E),
                    c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), _stream())
 
+    MOE_ROUTER_FEW_TOKENS = 64         # up to this many tokens the router's product and its choice are one launch
+
+    def moe_router(self, h, router, correction, top, scale, idx, weights) -> bool:
+        T, D = h.shape
+        E = correction.shape[0]
+        if T > self.MOE_ROUTER_FEW_TOKENS or (D + E) * 4 > 48 * 1024:
+            return False
+        _need(h, name="router input")
+        _need(router, h.dtype, (router.shape[0], D), "router weights")
+        if router.shape[0] < E:
+            _fail(f"router weights {tuple(router.shape)} for {E} experts")
+        _need(correction, name="router correction")
+        _need(idx, torch.int32, (T, top), "chosen experts")
+        _need(weights, torch.float32, (T, top), "expert weights")
+        self._call("moe", "gfb_moe_router", _ptr(h), _ptr(router), c_int(_dt(h)), _ptr(correction), c_int(_dt(correction)), c_int(E),
+                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), c_int(D), _stream())
+        return True
+
     def moe_experts(self, h, idx, weights, w13, w2, x, limit, alpha, shift=1.0):
         T, D = h.shape
         E, F2, _ = w13.shape

@@ -58,10 +58,8 @@ class MixtureOfExperts:
 
     def forward(self, h, residual):
         T = h.shape[0]
-        z = torch.empty(T, self.router.shape[0], dtype=torch.float32, device=h.device)
-        ops.linear(h, self.router, z)
         idx = torch.empty(T, self.top, dtype=torch.int32, device=h.device)
         w = torch.empty(T, self.top, dtype=torch.float32, device=h.device)
-        ops.moe_route(z, self.correction, self.top, self.router_scale, idx, w)
+        ops.moe_router(h, self.router, self.correction, self.top, self.router_scale, idx, w)
         x = as_residual(residual).tensor()                     # complete: the experts' kernel adds into it
         ops.moe_experts(h, idx, w, self.w13, self.w2, x, self.limit, self.alpha, self.shift)

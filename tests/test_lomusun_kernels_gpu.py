@@ -169,3 +169,28 @@ def test_experts_on_the_tensor_cores(T, E, top, F, D, limit):
     ops.check_status(ops.kernels().status)
     err = (x.cpu().double() - 0.25 - want).abs().max() / want.abs().max()
     assert float(err) < 6e-3, float(err)                      # one bfloat16 rounding of the activation, 32-bit sums
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,top,D", [(1, 5, 2, 40), (7, 40, 3, 200), (64, 130, 32, 72)])
+def test_router_in_one_launch(dtype, T, E, top, D):
+    """A decode step's router (logits and choice by one kernel) against sigmoid, correction, top and weights in 64-bit; the
+    correction decides a choice here and there, and the weights leave it out."""
+    g = torch.Generator().manual_seed(E)
+    h = torch.randn(T, D, generator=g).to(dtype)
+    router = (torch.randn(E, D, generator=g) * D ** -0.5).to(dtype)
+    corr = (torch.randn(E, generator=g) * 0.2).float()
+    pad = torch.cat([router, torch.zeros(-E % 8, D, dtype=dtype)])
+    idx = torch.empty(T, top, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, top, dtype=torch.float32, device="cuda")
+    assert ops.kernels().moe_router(h.cuda(), pad.cuda(), corr.cuda(), top, 1.7, idx, w)
+    s = torch.sigmoid(h.double() @ router.double().T)
+    choice = s + corr.double()
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: (-float(choice[t, e]), e))[:top]
+        gap = float(choice[t].sort(descending=True).values[top - 1] - choice[t].sort(descending=True).values[top]) if top < E else 1.0
+        if gap < 1e-3:
+            continue                                           # a close call may fall either way in bfloat16
+        assert sorted(idx[t].tolist()) == sorted(order), (t, idx[t].tolist(), order)
+        picked = s[t, idx[t].long().cpu()]
+        torch.testing.assert_close(w[t].cpu().double(), picked / picked.sum() * 1.7, rtol=2e-3, atol=1e-5)
