@@ -11,6 +11,9 @@
 //   swapped (decode, few tokens):   X = weights, Y = activations; the 128 MMA
 //            rows are weight rows, the tokens (padded to 16..128) are the MMA
 //            columns, so a step streams each weight byte once at full width.
+// Grouped products (a mixture of experts: every tile of tokens multiplies with the weights of its own expert, a row
+// offset into one tensor map over all experts) exist in the swapped form, in the normal form with a block per tile
+// and in the pair form: `gfb_gemm_tc_grouped`.
 // Epilogues: store (bf16 or f32), add into the 32-bit residual, SwiGLU over
 // weight rows that alternate gate/up, or (swapped only) a 32-bit partial for a
 // split over K that `splitk_reduce_kernel` sums in a fixed order.
