@@ -1,2 +1,2 @@
 """Architectures this library can build.  Importing the package registers them."""
-from . import llama, lasezen, gikepel, lomusun  # noqa: F401
+from . import llama, lasezen, gikepel, lomusun, tapupel  # noqa: F401

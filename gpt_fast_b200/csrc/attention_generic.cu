@@ -12,7 +12,12 @@
 // size `dv` of its own, values that are the leading part of the key rows, and a
 // bias on the scaled score that depends on head and distance n = p - j only:
 // `bias` (a table [bias_len][H], row min(n, bias_len - 1), added) and `slopes`
-// (one number per head, slopes[h] * n taken off).
+// (one number per head, slopes[h] * n taken off).  `softcap` > 0 squashes the (scaled, biased)
+// score to cap * tanh(score / cap).  `keep_first`: the sequence's first keep_first positions stay
+// visible to every later query whatever the window.  `maps` = 2: a head has two queries and a key
+// row two keys side by side, each pair a softmax of its own over the same values; the head's output
+// is o = o_1 - lambda o_2, divided by its root mean square over dv (diff_eps inside the root) and
+// multiplied by out_scale.
 //
 // One block per (token, query head).  Keys are visited in chunks of 128 that
 // start at multiples of 128 of the ABSOLUTE position, with an online softmax
@@ -32,7 +37,8 @@ __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedKV kv, GfbBatch b,
                          int H, int G, int d, int dv, int v_row, float scale, int window, int chunk,
                          const float* __restrict__ sink, const float* __restrict__ bias, int bias_len,
-                         const float* __restrict__ slopes, int* status) {
+                         const float* __restrict__ slopes, float softcap, int keep_first, int maps, float lambda,
+                         float diff_eps, float out_scale, int* status) {
     extern __shared__ float smem[];
     float* qs = smem;              // [d]
     float* ps = smem + d;          // [CHUNK]
@@ -46,25 +52,33 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
     int s = b.tok_seq[t];
     int slot = b.slots[s];
     int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
-    const T* qrow = q + ((size_t)t * H + h) * d;
-    for (int i = threadIdx.x; i < d; i += CHUNK) qs[i] = gfb_to_f32(qrow[i]) * scale;
+    const int dkr = d * maps;                    // numbers in a cached key row
 
     int lo = 0;
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
     if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
-    const size_t head_off = (size_t)g * kv.page_size * d, v_head_off = (size_t)g * kv.page_size * v_row;
-    const size_t page_stride = (size_t)G * kv.page_size * d, v_page_stride = (size_t)G * kv.page_size * v_row;
+    const size_t head_off = (size_t)g * kv.page_size * dkr, v_head_off = (size_t)g * kv.page_size * v_row;
+    const size_t page_stride = (size_t)G * kv.page_size * dkr, v_page_stride = (size_t)G * kv.page_size * v_row;
+    const int kept = lo > 0 ? min(keep_first, lo) : 0;       // positions [0, kept) are seen besides [lo, pos]
+    float first[MAX_DPT];                                    // the first map's finished output, while the second runs
+#pragma unroll
+    for (int i = 0; i < MAX_DPT; i++) first[i] = 0.f;
 
+  for (int map = 0; map < maps; map++) {
+    __syncthreads();               // every thread is done with the previous map's qs
+    const T* qrow = q + (((size_t)t * H + h) * maps + map) * d;
+    for (int i = threadIdx.x; i < d; i += CHUNK) qs[i] = gfb_to_f32(qrow[i]) * scale;
     float m_run = -INFINITY, l_run = 0.f;
     float acc[MAX_DPT];
 #pragma unroll
     for (int i = 0; i < MAX_DPT; i++) acc[i] = 0.f;
 
-    for (int c0 = (lo / CHUNK) * CHUNK; c0 <= pos; c0 += CHUNK) {
+    for (int c0 = kept > 0 ? 0 : (lo / CHUNK) * CHUNK; c0 <= pos; c0 += CHUNK) {
+        if (c0 >= kept && c0 + CHUNK <= lo) continue;          // a block of keys between the kept ones and the window
         __syncthreads();           // qs ready (first pass); ps / page_of free (later passes)
         int j = c0 + threadIdx.x;
-        bool live = j >= lo && j <= pos;
+        bool live = (j >= lo || j < kept) && j <= pos;
         int page = -1;
         if (live) {
             int pi = j / kv.page_size;
@@ -79,12 +93,13 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
         float sc = -INFINITY;
         if (live) {
             const T* krow = (const T*)kv.k_pool + (size_t)page * page_stride + head_off
-                            + (size_t)(j % kv.page_size) * d;
+                            + (size_t)(j % kv.page_size) * dkr + (size_t)map * d;
             float dot = 0.f;
             for (int i = 0; i < d; i++) dot = fmaf(qs[i], gfb_to_f32(krow[i]), dot);
             sc = dot;
             if (bias != nullptr) sc += bias[(size_t)min(pos - j, bias_len - 1) * H + h];
             if (slopes != nullptr) sc -= slopes[h] * (float)(pos - j);
+            if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
         }
         float m_new = fmaxf(m_run, gfb_block_max(sc, scratch));
         float p = live ? expf(sc - m_new) : 0.f;
@@ -120,12 +135,35 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
         for (int r = 0; r < MAX_DPT; r++) acc[r] *= corr;
     }
     float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    T* orow = out + ((size_t)t * H + h) * dv;
+    if (maps == 1) {
+        T* orow = out + ((size_t)t * H + h) * dv;
 #pragma unroll
-    for (int r = 0; r < MAX_DPT; r++) {
-        int dim = threadIdx.x + r * CHUNK;
-        if (dim < dv) orow[dim] = gfb_from_f32<T>(acc[r] * inv);
+        for (int r = 0; r < MAX_DPT; r++) {
+            int dim = threadIdx.x + r * CHUNK;
+            if (dim < dv) orow[dim] = gfb_from_f32<T>(acc[r] * inv);
+        }
+    } else if (map == 0) {
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) first[r] = acc[r] * inv;
+    } else {
+        // the difference of the two maps, normed over the head and scaled
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) {
+            first[r] -= lambda * (acc[r] * inv);
+            if (threadIdx.x + r * CHUNK < dv) ss += first[r] * first[r];
+        }
+        __syncthreads();
+        ss = gfb_block_sum(ss, scratch);
+        const float f = out_scale / sqrtf(ss / (float)dv + diff_eps);
+        T* orow = out + ((size_t)t * H + h) * dv;
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) {
+            int dim = threadIdx.x + r * CHUNK;
+            if (dim < dv) orow[dim] = gfb_from_f32<T>(first[r] * f);
+        }
     }
+  }
 }
 
 GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
@@ -134,8 +172,13 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
                                   const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
                                   int n_seqs, int n_tokens, int H, int G, int d, int dv, float scale, int window,
                                   int chunk, const float* sink, int values_in_keys, const float* bias, int bias_len,
-                                  const float* slopes, int* status, cudaStream_t stream) {
+                                  const float* slopes, float softcap, int keep_first, int maps, float lambda, float diff_eps,
+                                  float out_scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (maps != 1 && maps != 2) return gfb_fail("gfb_attention_generic: %d score maps per head (1 or 2)", maps);
+    if (keep_first < 0) return gfb_fail("gfb_attention_generic: %d kept first positions", keep_first);
+    if (keep_first > 0 && chunk > 0) return gfb_fail("gfb_attention_generic: kept first positions go with a window, not with a block mask");
+    if (maps == 2 && (values_in_keys || sink != nullptr)) return gfb_fail("gfb_attention_generic: two maps take values of their own and no sink");
     if (dv <= 0) dv = d;
     if (dv > CHUNK * MAX_DPT) return gfb_fail("gfb_attention_generic: value head size %d exceeds %d", dv, CHUNK * MAX_DPT);
     if (G <= 0 || H % G) return gfb_fail("gfb_attention_generic: %d heads do not divide into %d groups", H, G);
@@ -152,10 +195,10 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream,
-                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, status);
+                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, softcap, keep_first, maps, lambda, diff_eps, out_scale, status);
     else if (dt == GFB_F32)
         e = gfb_launch(attention_generic_kernel<float>, grid, dim3(CHUNK), smem, stream,
-                       (const float*)q, (float*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, status);
+                       (const float*)q, (float*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, bias, bias_len, slopes, softcap, keep_first, maps, lambda, diff_eps, out_scale, status);
     else
         return gfb_fail("gfb_attention_generic: unknown type %d", dt);
     return gfb_check(e, "gfb_attention_generic");

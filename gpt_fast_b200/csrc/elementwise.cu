@@ -35,8 +35,8 @@ GFB_API int gfb_activation(const void* x, void* out, int dt, long n, int kind, c
 }
 
 // y[t, c] *= sigmoid(gate[t, gate_off + c / group])
-template <typename T>
-__global__ void sigmoid_gate_kernel(T* __restrict__ y, const T* __restrict__ gate, int C, int ld_gate, int gate_off, int group, size_t n) {
+template <typename T, typename TG>
+__global__ void sigmoid_gate_kernel(T* __restrict__ y, const TG* __restrict__ gate, int C, int ld_gate, int gate_off, int group, size_t n) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -47,15 +47,17 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ y, const T* __restrict__ gat
     y[i] = gfb_from_f32<T>(gfb_to_f32(y[i]) / (1.0f + expf(-z)));
 }
 
-// y [T, C] and gate [T, ld_gate] of type dt; the gates of a row start at column gate_off, one per `group` columns of y.
-GFB_API int gfb_sigmoid_gate(void* y, const void* gate, int dt, int T, int C, int ld_gate, int gate_off, int group, cudaStream_t stream) {
+// y [T, C] of type dt and gate [T, ld_gate] of type gate_dt (dt, or 32-bit); the gates of a row start at column gate_off, one per
+// `group` columns of y.
+GFB_API int gfb_sigmoid_gate(void* y, const void* gate, int dt, int gate_dt, int T, int C, int ld_gate, int gate_off, int group, cudaStream_t stream) {
     const size_t n = (size_t)T * C;
     if (n == 0) return 0;
     if (group < 1 || C % group) return gfb_fail("gfb_sigmoid_gate: groups of %d columns in rows of %d", group, C);
     const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaError_t e;
-    if (dt == GFB_BF16) e = gfb_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)gate, C, ld_gate, gate_off, group, n);
-    else if (dt == GFB_F32) e = gfb_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)y, (const float*)gate, C, ld_gate, gate_off, group, n);
-    else return gfb_fail("gfb_sigmoid_gate: unknown type %d", dt);
+    if (dt == GFB_BF16 && gate_dt == GFB_BF16) e = gfb_launch(sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)gate, C, ld_gate, gate_off, group, n);
+    else if (dt == GFB_BF16 && gate_dt == GFB_F32) e = gfb_launch(sigmoid_gate_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)y, (const float*)gate, C, ld_gate, gate_off, group, n);
+    else if (dt == GFB_F32 && gate_dt == GFB_F32) e = gfb_launch(sigmoid_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)y, (const float*)gate, C, ld_gate, gate_off, group, n);
+    else return gfb_fail("gfb_sigmoid_gate: unsupported types %d and %d", dt, gate_dt);
     return gfb_check(e, "gfb_sigmoid_gate");
 }

@@ -10,7 +10,8 @@
 // so that the norm behind a sublayer and the norm ahead of the next one cost one trip over the row.
 // Means and variances are 32-bit; the variance is the mean of the squared deviations (two passes
 // over the row, which sits in shared memory).  `rms` = 1 selects the root-mean-square form (no
-// mean, no bias) with the same interface.
+// mean, no bias) with the same interface.  Without a weight for (2) the output is the row itself in
+// the compute type: a sublayer that reads the stream as it is.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -65,8 +66,12 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
     }
     if (out == nullptr) return;
     __syncthreads();
-    const float2 st = row_stats(row, D, eps, rms, scratch);
     TO* o = out + (size_t)r * D;
+    if (w == nullptr) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_from_f32<TO>(row[i]);
+        return;
+    }
+    const float2 st = row_stats(row, D, eps, rms, scratch);
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float n = (row[i] - st.x) * st.y * ld_w(w, w_dt, i);
         if (!rms && b != nullptr) n += ld_w(b, w_dt, i);
@@ -171,15 +176,15 @@ layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, 
         }
     }
     if (out == nullptr) return;
-    const float2 st = reg_stats(v, nvec, D, eps, rms, scratch);
+    const float2 st = w == nullptr ? make_float2(0.f, 1.f) : reg_stats(v, nvec, D, eps, rms, scratch);
 #pragma unroll
     for (int k = 0; k < NV; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < nvec) {
-            const float4 g = ld_w4(w, w_dt, i);
+            const float4 g = w == nullptr ? make_float4(1.f, 1.f, 1.f, 1.f) : ld_w4(w, w_dt, i);
             float4 n = make_float4((v[k].x - st.x) * st.y * g.x, (v[k].y - st.x) * st.y * g.y,
                                    (v[k].z - st.x) * st.y * g.z, (v[k].w - st.x) * st.y * g.w);
-            if (!rms && b != nullptr) { const float4 c = ld_w4(b, w_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
+            if (!rms && b != nullptr && w != nullptr) { const float4 c = ld_w4(b, w_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
             TO* o = out + (size_t)r * D + 4 * i;
             if (sizeof(TO) == 4) {
                 *reinterpret_cast<float4*>(o) = n;

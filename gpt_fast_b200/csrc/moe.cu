@@ -2,7 +2,8 @@
 //
 // gfb_moe_router        few tokens: router logits and choice in one launch (a block per token)
 // gfb_moe_route         from 32-bit router logits: s = sigmoid(z); the `top` experts with the largest s + correction
-//                       (lowest index on ties); weights s / (sum of the chosen s + 1e-20) * scale
+//                       (lowest index on ties); weights s / (sum of the chosen s + 1e-20) * scale.  Or (mode ROUTE_SOFTMAX_TOP)
+//                       the `top` largest logits themselves, weighted by the softmax over just those, times scale
 // gfb_moe_glu           act[pair, f] = g * sigmoid(alpha g) * (u + shift),  g = min(gate_f . h, limit),
 //                       u = clamp(up_f . h, -limit, limit), for every (token, chosen expert) pair
 // gfb_moe_down          x[t] += sum over the token's chosen experts of weight * (W_down act[pair]); 32-bit sum into the stream
@@ -30,16 +31,17 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 // ------------------------------------------------------------------------------------ router ----
 constexpr int MAX_EPL = 16;           // experts per lane: E <= 512
 constexpr int ROUTE_WARPS = 4;
+enum { ROUTE_SIGMOID = 0, ROUTE_SOFTMAX_TOP = 1 };
 
 // one token's choice by one warp: `logits` are the token's E router logits
 __device__ __forceinline__ void route_token(const float* __restrict__ logits, const void* __restrict__ correction, int c_dt, int E, int top,
-                                            float scale, int* __restrict__ idx, float* __restrict__ weights, int lane) {
+                                            float scale, int* __restrict__ idx, float* __restrict__ weights, int lane, int mode) {
     float s[MAX_EPL], c[MAX_EPL];
 #pragma unroll
     for (int i = 0; i < MAX_EPL; i++) {
         const int e = lane + 32 * i;
         if (e < E) {
-            s[i] = sigmoid_f(logits[e]);
+            s[i] = mode == ROUTE_SOFTMAX_TOP ? logits[e] : sigmoid_f(logits[e]);
             c[i] = s[i] + (correction != nullptr ? ldw(correction, c_dt, e) : 0.f);
         } else {
             s[i] = 0.f;
@@ -47,6 +49,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, co
         }
     }
     float sum = 0.f, mine = 0.f;       // lane r keeps the r-th chosen score
+    float first = 0.f;                 // the largest chosen logit (softmax over the chosen ones)
     int mine_e = 0;
     for (int r = 0; r < top; r++) {
         float best = -INFINITY, best_s = 0.f;
@@ -63,33 +66,37 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, co
 #pragma unroll
         for (int i = 0; i < MAX_EPL; i++)
             if (lane + 32 * i == best_e) c[i] = -INFINITY;
+        if (mode == ROUTE_SOFTMAX_TOP) {
+            if (r == 0) first = best_s;
+            best_s = expf(best_s - first);
+        }
         sum += best_s;
         if (lane == r) { mine = best_s; mine_e = best_e; }
     }
     if (lane < top) {
         idx[lane] = mine_e;
-        weights[lane] = mine / (sum + 1e-20f) * scale;
+        weights[lane] = mode == ROUTE_SOFTMAX_TOP ? mine / sum * scale : mine / (sum + 1e-20f) * scale;
     }
 }
 
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_route_kernel(const float* __restrict__ logits, int ld, const void* __restrict__ correction, int c_dt, int E, int top,
-                 float scale, int* __restrict__ idx, float* __restrict__ weights, int T) {
+                 float scale, int* __restrict__ idx, float* __restrict__ weights, int T, int mode) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
     if (t >= T) return;
-    route_token(logits + (size_t)t * ld, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane);
+    route_token(logits + (size_t)t * ld, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane, mode);
 }
 
 GFB_API int gfb_moe_route(const float* logits, int ld, const void* correction, int c_dt, int E, int top, float scale, int* idx,
-                          float* weights, int T, cudaStream_t stream) {
+                          float* weights, int T, int mode, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E < 1 || E > 32 * MAX_EPL) return gfb_fail("gfb_moe_route: %d experts (1 to %d)", E, 32 * MAX_EPL);
     if (top < 1 || top > 32 || top > E) return gfb_fail("gfb_moe_route: %d of %d experts per token (1 to 32)", top, E);
     cudaError_t e = gfb_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(32 * ROUTE_WARPS), 0, stream, logits, ld,
-                               correction, c_dt, E, top, scale, idx, weights, T);
+                               correction, c_dt, E, top, scale, idx, weights, T, mode);
     return gfb_check(e, "gfb_moe_route");
 }
 
@@ -128,8 +135,8 @@ constexpr int ROUTER_WARPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTER_WARPS)
 moe_router_kernel(const T* __restrict__ h, const T* __restrict__ router, const void* __restrict__ correction, int c_dt, int E, int top,
-                  float scale, int* __restrict__ idx, float* __restrict__ weights, int D) {
-    extern __shared__ __align__(16) float rs[];        // the input [D], then the logits [E]
+                  float scale, int* __restrict__ idx, float* __restrict__ weights, int D, int mode, int n_extra, float* __restrict__ extra) {
+    extern __shared__ __align__(16) float rs[];        // the input [D], then the logits [E + n_extra]
     float* z = rs + D;
     gfb_pdl_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -138,29 +145,34 @@ moe_router_kernel(const T* __restrict__ h, const T* __restrict__ router, const v
     for (int i = threadIdx.x; i < D; i += blockDim.x) rs[i] = gfb_to_f32(h[(size_t)t * D + i]);
     __syncthreads();
     const bool wide = rows_wide(router, D);
-    for (int e = warp; e < E; e += ROUTER_WARPS) {
+    for (int e = warp; e < E + n_extra; e += ROUTER_WARPS) {
         const float d = row_dot(router + (size_t)e * D, rs, D, lane, wide);
-        if (lane == 0) z[e] = d;
+        if (lane == 0) {
+            z[e] = d;
+            if (e >= E) extra[(size_t)t * n_extra + (e - E)] = d;      // rows behind the experts': their logits are handed out as they are
+        }
     }
     __syncthreads();
-    if (warp == 0) route_token(z, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane);
+    if (warp == 0) route_token(z, correction, c_dt, E, top, scale, idx + (size_t)t * top, weights + (size_t)t * top, lane, mode);
 }
 
-// h [T, D] and router [>= E, D] of type dt (rows beyond E are padding); few tokens only: a block per token
+// h [T, D] and router [>= E + n_extra, D] of type dt (further rows are padding); few tokens only: a block per token.
+// The logits of the n_extra rows behind the experts' go to extra float32 [T, n_extra].
 GFB_API int gfb_moe_router(const void* h, const void* router, int dt, const void* correction, int c_dt, int E, int top, float scale,
-                           int* idx, float* weights, int T, int D, cudaStream_t stream) {
+                           int* idx, float* weights, int T, int D, int mode, int n_extra, float* extra, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E < 1 || E > 32 * MAX_EPL) return gfb_fail("gfb_moe_router: %d experts (1 to %d)", E, 32 * MAX_EPL);
     if (top < 1 || top > 32 || top > E) return gfb_fail("gfb_moe_router: %d of %d experts per token (1 to 32)", top, E);
-    const size_t smem = (size_t)(D + E) * sizeof(float);
+    if (n_extra < 0 || (n_extra > 0 && extra == nullptr)) return gfb_fail("gfb_moe_router: %d further rows without a place for their logits", n_extra);
+    const size_t smem = (size_t)(D + E + n_extra) * sizeof(float);
     if (smem > 48 * 1024) return gfb_fail("gfb_moe_router: %zu bytes of shared memory", smem);
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(moe_router_kernel<__nv_bfloat16>, dim3((unsigned)T), dim3(32 * ROUTER_WARPS), smem, stream, (const __nv_bfloat16*)h,
-                       (const __nv_bfloat16*)router, correction, c_dt, E, top, scale, idx, weights, D);
+                       (const __nv_bfloat16*)router, correction, c_dt, E, top, scale, idx, weights, D, mode, n_extra, extra);
     else if (dt == GFB_F32)
         e = gfb_launch(moe_router_kernel<float>, dim3((unsigned)T), dim3(32 * ROUTER_WARPS), smem, stream, (const float*)h, (const float*)router,
-                       correction, c_dt, E, top, scale, idx, weights, D);
+                       correction, c_dt, E, top, scale, idx, weights, D, mode, n_extra, extra);
     else return gfb_fail("gfb_moe_router: unknown type %d", dt);
     return gfb_check(e, "gfb_moe_router");
 }

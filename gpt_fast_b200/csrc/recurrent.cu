@@ -10,6 +10,11 @@
 //                   g = exp(-exp(A_log_h) softplus(a_raw + dt_bias))
 // gfb_gated_norm    root-mean-square norm over groups of columns with a weight and a gate (SiLU or sigmoid) that
 //                   is applied before or behind the norm
+// gfb_rglru         a gated linear recurrence per channel (the real-gated linear recurrent unit): with the channels in
+//                   equal blocks and a square matrix per block and gate,
+//                       r = sigmoid(Wa_b u_b + ba),  i = sigmoid(Wi_b u_b + bi),  a = exp(-c r softplus(lam)),
+//                       S <- a S + sqrt(1 - a^2) i u,   out = S * gelu_tanh(y + by)
+//                   S one number per channel and sequence, 32-bit
 //
 // The two recurrences share one layout: a block owns one (sequence, head) and a slice of the state's columns and
 // walks through the sequence's tokens of this step; a lane keeps RPT rows of one column of S in registers.  Sums
@@ -32,8 +37,8 @@ constexpr int MAX_TAPS = 16;
 // state of a slot: [taps - 1][C] inputs, oldest first, at state + slot * state_ld
 template <typename T>
 __global__ void short_conv_kernel(const T* __restrict__ src, int ld, int col_off, int C, const void* __restrict__ w,
-                                  const void* __restrict__ bias, int w_dt, int taps, const float* __restrict__ state,
-                                  size_t state_ld, float* __restrict__ out, GfbBatch b, int act) {
+                                  const void* __restrict__ bias, const void* __restrict__ in_bias, int w_dt, int taps,
+                                  const float* __restrict__ state, size_t state_ld, float* __restrict__ out, GfbBatch b, int act) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int t = blockIdx.x;
@@ -43,10 +48,11 @@ __global__ void short_conv_kernel(const T* __restrict__ src, int ld, int col_off
     const int i = t - b.cu_seqlens[s];
     const float* st = state + (size_t)b.slots[s] * state_ld;
     float acc = bias != nullptr ? ldw(bias, w_dt, c) : 0.f;
+    const float ib = in_bias != nullptr ? ldw(in_bias, w_dt, c) : 0.f;       // part of every real input, not of the zeros ahead of a sequence
     for (int j = 0; j < taps; j++) {
         const int back = taps - 1 - j;
         float v;
-        if (i - back >= 0) v = gfb_to_f32(src[(size_t)(t - back) * ld + col_off + c]);
+        if (i - back >= 0) v = gfb_to_f32(src[(size_t)(t - back) * ld + col_off + c]) + ib;
         else v = st[(size_t)(taps - 1 + i - back) * C + c];
         acc = fmaf(ldw(w, w_dt, (size_t)c * taps + j), v, acc);
     }
@@ -54,8 +60,8 @@ __global__ void short_conv_kernel(const T* __restrict__ src, int ld, int col_off
 }
 
 template <typename T>
-__global__ void conv_state_kernel(const T* __restrict__ src, int ld, int col_off, int C, int taps, float* __restrict__ state,
-                                  size_t state_ld, GfbBatch b) {
+__global__ void conv_state_kernel(const T* __restrict__ src, int ld, int col_off, int C, const void* __restrict__ in_bias, int w_dt,
+                                  int taps, float* __restrict__ state, size_t state_ld, GfbBatch b) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x;
@@ -64,11 +70,12 @@ __global__ void conv_state_kernel(const T* __restrict__ src, int ld, int col_off
     const int t0 = b.cu_seqlens[s], n = b.cu_seqlens[s + 1] - t0;
     float* st = state + (size_t)b.slots[s] * state_ld;
     float keep[MAX_TAPS];
+    const float ib = in_bias != nullptr ? ldw(in_bias, w_dt, c) : 0.f;
 #pragma unroll
     for (int k = 0; k < MAX_TAPS; k++) {
         if (k < taps - 1) {
             const int i = n - (taps - 1) + k;                   // index among this step's tokens; negative: older
-            keep[k] = i >= 0 ? gfb_to_f32(src[(size_t)(t0 + i) * ld + col_off + c]) : st[(size_t)(taps - 1 + i) * C + c];
+            keep[k] = i >= 0 ? gfb_to_f32(src[(size_t)(t0 + i) * ld + col_off + c]) + ib : st[(size_t)(taps - 1 + i) * C + c];
         }
     }
 #pragma unroll
@@ -78,8 +85,9 @@ __global__ void conv_state_kernel(const T* __restrict__ src, int ld, int col_off
 
 // src [T, ld] of type dt, C channels from column col_off; w [C, taps] and bias [C] (or null) of type w_dt;
 // state float32, slot stride state_ld, (taps - 1) * C numbers per slot; out float32 [T, C]; act: 1 = SiLU, 0 = none.
+// in_bias [C] (or null) is added to every input before the taps (the state keeps the sums).
 // The state is advanced by a second kernel behind the first.
-GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, const void* w, const void* bias, int w_dt,
+GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, const void* w, const void* bias, const void* in_bias, int w_dt,
                            int taps, float* state, long state_ld, float* out, const int* cu_seqlens, const int* tok_seq,
                            const int* slots, const int* lengths, int n_seqs, int n_tokens, int act, cudaStream_t stream) {
     if (n_tokens <= 0 || C <= 0) return 0;
@@ -91,19 +99,19 @@ GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, 
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(short_conv_kernel<__nv_bfloat16>, dim3(n_tokens, cb), dim3(threads), 0, stream, (const __nv_bfloat16*)src, ld,
-                       col_off, C, w, bias, w_dt, taps, (const float*)state, (size_t)state_ld, out, b, act);
+                       col_off, C, w, bias, in_bias, w_dt, taps, (const float*)state, (size_t)state_ld, out, b, act);
     else if (dt == GFB_F32)
         e = gfb_launch(short_conv_kernel<float>, dim3(n_tokens, cb), dim3(threads), 0, stream, (const float*)src, ld, col_off, C, w,
-                       bias, w_dt, taps, (const float*)state, (size_t)state_ld, out, b, act);
+                       bias, in_bias, w_dt, taps, (const float*)state, (size_t)state_ld, out, b, act);
     else
         return gfb_fail("gfb_short_conv: unknown type %d", dt);
     if (gfb_check(e, "gfb_short_conv")) return 1;
     if (taps == 1) return 0;
     if (dt == GFB_BF16)
         e = gfb_launch(conv_state_kernel<__nv_bfloat16>, dim3(n_seqs, cb), dim3(threads), 0, stream, (const __nv_bfloat16*)src, ld,
-                       col_off, C, taps, state, (size_t)state_ld, b);
+                       col_off, C, in_bias, w_dt, taps, state, (size_t)state_ld, b);
     else
-        e = gfb_launch(conv_state_kernel<float>, dim3(n_seqs, cb), dim3(threads), 0, stream, (const float*)src, ld, col_off, C, taps,
+        e = gfb_launch(conv_state_kernel<float>, dim3(n_seqs, cb), dim3(threads), 0, stream, (const float*)src, ld, col_off, C, in_bias, w_dt, taps,
                        state, (size_t)state_ld, b);
     return gfb_check(e, "gfb_short_conv (state)");
 }
@@ -581,4 +589,148 @@ GFB_API int gfb_gated_norm(const float* y, const void* gate, int gate_dt, int ld
     else return gfb_fail("gfb_gated_norm: unsupported types gate %d out %d", gate_dt, out_dt);
 #undef GO
     return gfb_check(e, "gfb_gated_norm");
+}
+
+// ------------------------------------------------------------------------------ gated linear recurrence ----
+// Two kernels.  The gates of all tokens at once: a block takes a tile of RG_TOKENS tokens of one channel block, stages their
+// inputs in shared memory (transposed, so that a thread reads four tokens of one input with one load) and each thread owns one
+// output channel of the block for both gates: per input one weight of each gate (the matrices are stored [block][in][out], so a
+// warp reads consecutive outputs) against the tile's tokens.  It leaves a and b = sqrt(1 - a^2) i u per token and channel.
+// Then the recurrence: a thread per (sequence, channel) walks through the sequence's tokens of this step, S <- a S + b, and writes
+// S gelu_tanh(y + by).  A number's sums do not depend on how the sequence was cut or batched.
+constexpr int RG_TOKENS = 16;
+constexpr int RG_THREADS = 128;
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const TW* __restrict__ wi, const void* __restrict__ ba,
+                   const void* __restrict__ bi, const void* __restrict__ lam, int v_dt, float decay_scale, float* __restrict__ a_out,
+                   float* __restrict__ b_out, int T, int C, int bw) {
+    extern __shared__ __align__(16) float us[];          // [bw][RG_TOKENS]
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t0 = blockIdx.x * RG_TOKENS, blk = blockIdx.y;
+    const int o = blockIdx.z * RG_THREADS + threadIdx.x;
+    const int nt = min(RG_TOKENS, T - t0);
+    for (int e = threadIdx.x; e < bw * RG_TOKENS; e += RG_THREADS) {
+        const int tt = e / bw, i = e - tt * bw;         // consecutive threads read consecutive inputs of one token
+        us[i * RG_TOKENS + tt] = tt < nt ? u[(size_t)(t0 + tt) * C + blk * bw + i] : 0.f;
+    }
+    __syncthreads();
+    if (o >= bw) return;
+    float ra[RG_TOKENS], ri[RG_TOKENS];
+#pragma unroll
+    for (int k = 0; k < RG_TOKENS; k++) ra[k] = ri[k] = 0.f;
+    const TW* pa = wa + (size_t)blk * bw * bw + o;
+    const TW* pi = wi + (size_t)blk * bw * bw + o;
+#pragma unroll 4
+    for (int i = 0; i < bw; i++) {
+        const float xa = gfb_to_f32(pa[(size_t)i * bw]), xi = gfb_to_f32(pi[(size_t)i * bw]);
+        const float4* row = reinterpret_cast<const float4*>(us + i * RG_TOKENS);
+#pragma unroll
+        for (int k4 = 0; k4 < RG_TOKENS / 4; k4++) {
+            const float4 v = row[k4];
+            ra[4 * k4 + 0] = fmaf(xa, v.x, ra[4 * k4 + 0]); ri[4 * k4 + 0] = fmaf(xi, v.x, ri[4 * k4 + 0]);
+            ra[4 * k4 + 1] = fmaf(xa, v.y, ra[4 * k4 + 1]); ri[4 * k4 + 1] = fmaf(xi, v.y, ri[4 * k4 + 1]);
+            ra[4 * k4 + 2] = fmaf(xa, v.z, ra[4 * k4 + 2]); ri[4 * k4 + 2] = fmaf(xi, v.z, ri[4 * k4 + 2]);
+            ra[4 * k4 + 3] = fmaf(xa, v.w, ra[4 * k4 + 3]); ri[4 * k4 + 3] = fmaf(xi, v.w, ri[4 * k4 + 3]);
+        }
+    }
+    const int c = blk * bw + o;
+    const float bias_a = ldw(ba, v_dt, c), bias_i = ldw(bi, v_dt, c);
+    const float rate = decay_scale * softplus_f(ldw(lam, v_dt, c));
+#pragma unroll
+    for (int k = 0; k < RG_TOKENS; k++) {
+        if (k < nt) {
+            const float r = sigmoid_f(ra[k] + bias_a), g = sigmoid_f(ri[k] + bias_i);
+            const float log_a = -rate * r;
+            const size_t at = (size_t)(t0 + k) * C + c;
+            a_out[at] = expf(log_a);
+            b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * g * us[o * RG_TOKENS + k];
+        }
+    }
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ bb, const TY* __restrict__ y, int ld_y, int y_off,
+                  const void* __restrict__ y_bias, int v_dt, float* __restrict__ state, size_t state_ld, TO* __restrict__ out,
+                  GfbBatch b, int C) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * RG_THREADS + threadIdx.x;
+    if (c >= C) return;
+    const int t0 = b.cu_seqlens[s], n = b.cu_seqlens[s + 1] - t0;
+    float* st = state + (size_t)b.slots[s] * state_ld + c;
+    const float yb = y_bias != nullptr ? ldw(y_bias, v_dt, c) : 0.f;
+    float S = *st;
+    constexpr int U = 8;
+    for (int i0 = 0; i0 < n; i0 += U) {
+        float av[U], bv[U], yv[U];
+#pragma unroll
+        for (int k = 0; k < U; k++) {
+            const int t = t0 + min(i0 + k, n - 1);
+            av[k] = a[(size_t)t * C + c];
+            bv[k] = bb[(size_t)t * C + c];
+            yv[k] = gfb_to_f32(y[(size_t)t * ld_y + y_off + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < U; k++) {
+            if (i0 + k < n) {
+                S = fmaf(av[k], S, bv[k]);
+                out[(size_t)(t0 + i0 + k) * C + c] = gfb_from_f32<TO>(S * gelu_tanh_f(yv[k] + yb));
+            }
+        }
+    }
+    *st = S;
+}
+
+// u float32 [T, C]: the recurrence's inputs.  wa, wi [blocks][C / blocks (in)][C / blocks (out)] of type w_dt: the two gates'
+// matrices, transposed per block.  ba, bi, lam, y_bias [C] of type v_dt.  y [T, ld_y] of type y_dt, its C columns from y_off.
+// state float32, slot stride state_ld, C numbers per slot.  out [T, C] of type out_dt.  scratch float32 [2][T][C].
+GFB_API int gfb_rglru(const float* u, const void* wa, const void* wi, int w_dt, const void* ba, const void* bi, const void* lam,
+                      const void* y_bias, int v_dt, float decay_scale, const void* y, int y_dt, int ld_y, int y_off, float* state,
+                      long state_ld, void* out, int out_dt, float* scratch, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                      const int* lengths, int n_seqs, int n_tokens, int C, int blocks, cudaStream_t stream) {
+    if (n_tokens <= 0 || C <= 0) return 0;
+    if (blocks < 1 || C % blocks) return gfb_fail("gfb_rglru: %d channels do not divide into %d blocks", C, blocks);
+    const int bw = C / blocks;
+    const size_t smem = (size_t)bw * RG_TOKENS * sizeof(float);
+    if (smem > 200 * 1024) return gfb_fail("gfb_rglru: blocks of %d channels exceed the kernel's shared memory", bw);
+    if (blocks > 65535 || (bw + RG_THREADS - 1) / RG_THREADS > 65535) return gfb_fail("gfb_rglru: too many blocks");
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    float* a_buf = scratch;
+    float* b_buf = scratch + (size_t)n_tokens * C;
+    const dim3 grid((n_tokens + RG_TOKENS - 1) / RG_TOKENS, blocks, (bw + RG_THREADS - 1) / RG_THREADS);
+    cudaError_t e;
+#define GATES(TW)                                                                                                              \
+    do {                                                                                                                       \
+        static size_t allowed = 48 * 1024;                                                                                     \
+        if (smem > allowed) {                                                                                                  \
+            cudaFuncSetAttribute(rglru_gates_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);             \
+            allowed = 200 * 1024;                                                                                              \
+        }                                                                                                                      \
+        e = gfb_launch(rglru_gates_kernel<TW>, grid, dim3(RG_THREADS), smem, stream, u, (const TW*)wa, (const TW*)wi, ba, bi, lam, \
+                       v_dt, decay_scale, a_buf, b_buf, n_tokens, C, bw);                                                      \
+    } while (0)
+    if (w_dt == GFB_BF16) GATES(__nv_bfloat16);
+    else if (w_dt == GFB_F32) GATES(float);
+    else return gfb_fail("gfb_rglru: unknown weight type %d", w_dt);
+#undef GATES
+    if (gfb_check(e, "gfb_rglru (gates)")) return 1;
+    const dim3 sgrid(n_seqs, (C + RG_THREADS - 1) / RG_THREADS);
+    typedef __nv_bfloat16 bf16;
+#define SCAN(TY, TO) e = gfb_launch(rglru_scan_kernel<TY, TO>, sgrid, dim3(RG_THREADS), 0, stream, (const float*)a_buf, (const float*)b_buf, \
+                                    (const TY*)y, ld_y, y_off, y_bias, v_dt, state, (size_t)state_ld, (TO*)out, b, C)
+    if (y_dt == GFB_BF16 && out_dt == GFB_BF16) SCAN(bf16, bf16);
+    else if (y_dt == GFB_F32 && out_dt == GFB_F32) SCAN(float, float);
+    else if (y_dt == GFB_F32 && out_dt == GFB_BF16) SCAN(float, bf16);
+    else return gfb_fail("gfb_rglru: unsupported types y %d out %d", y_dt, out_dt);
+#undef SCAN
+    return gfb_check(e, "gfb_rglru (scan)");
 }

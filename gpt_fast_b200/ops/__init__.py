@@ -125,7 +125,7 @@ def layernorm(x, weight, bias, eps: float, out, rows=None, branch=None, rms: boo
     branch = (y, weight, bias, eps, mult), only without rows: the kernel first completes
     x += mult * norm(y) with that norm's parameters (written back), y being a float32 [T, D] tensor or partial sums
     [S, T, D] of it, and then norms the new x into `out` (if given).  rms=True: the root-mean-square form, no mean
-    and no bias, for both norms."""
+    and no bias, for both norms.  weight=None with an `out`: no norm at all, out = the (new) x in the compute type."""
     return kernels().layernorm(x, weight, bias, eps, out, rows, branch, rms)
 
 
@@ -158,12 +158,27 @@ def headwise_linear(a, w, out, n_head: int, k: int, n: int, a_off: int = 0, a_st
     return kernels().headwise_linear(a, w, out, n_head, k, n, a_off, a_stride, out_off, out_stride, gate, gate_off)
 
 
-def short_conv(src, col_off: int, channels: int, weight, bias, state, state_off: int, out, batch: BatchMeta, act: bool = True):
+def short_conv(src, col_off: int, channels: int, weight, bias, state, state_off: int, out, batch: BatchMeta, act: bool = True,
+               in_bias=None):
     """Causal convolution over time per channel, then SiLU (act).  src [T, W]: the channels start at column col_off;
     weight [channels, taps], whose last column meets the current token; bias [channels] or None; out float32 [T,
     channels].  state float32 [n_slots, S]: from column state_off, the (taps - 1) * channels latest inputs of each
-    sequence, oldest first (zeros at a sequence's start); read for the tokens at a step's start and advanced."""
-    return kernels().short_conv(src, col_off, channels, weight, bias, state, state_off, out, batch, act)
+    sequence, oldest first (zeros at a sequence's start); read for the tokens at a step's start and advanced.
+    in_bias [channels]: added to every input ahead of the taps (a projection's bias; the zeros before a sequence's start
+    stay zeros, and the state keeps the sums)."""
+    if in_bias is None:
+        return kernels().short_conv(src, col_off, channels, weight, bias, state, state_off, out, batch, act)
+    return kernels().short_conv(src, col_off, channels, weight, bias, state, state_off, out, batch, act, in_bias=in_bias)
+
+
+def rglru(u, w_a, w_i, b_a, b_i, lam, decay_scale: float, y_src, y_off: int, y_bias, state, state_off: int, out, batch: BatchMeta):
+    """A gated linear recurrence per channel, token after token.  The C channels are `blocks` equal parts; per part b
+    r = sigmoid(u_b Wa_b + ba_b), i = sigmoid(u_b Wi_b + bi_b);  a = exp(-decay_scale r softplus(lam));
+    S <- a S + sqrt(1 - a^2) i u;  out = S * gelu_tanh(y + y_bias).
+    u float32 [T, C]; w_a, w_i [blocks, C / blocks (in), C / blocks (out)]; b_a, b_i, lam, y_bias [C] of one type;
+    y = y_src[:, y_off : y_off + C]; state float32 [n_slots, S] holds S (C numbers per sequence) from column state_off;
+    out [T, C] in the compute type.  Gates, decay and state are 32-bit."""
+    return kernels().rglru(u, w_a, w_i, b_a, b_i, lam, decay_scale, y_src, y_off, y_bias, state, state_off, out, batch)
 
 
 def ssd_scan(x, b_off: int, c_off: int, dt_src, dt_off: int, dt_bias, a_log, skip, state, state_off: int, out,
@@ -205,14 +220,22 @@ def gated_norm(y, gate, gate_off: int, weight, out, group: int, eps: float, act:
 
 def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, n_kv: int, head_dim: int,
                 v_head_dim: int, table=None, rot_dims: int = 0, pairing: str = "half", q_norm=None, k_norm=None,
-                norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True, norm_whole: bool = False):
+                norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True, norm_whole: bool = False,
+                norm_bare: bool = False, norm_last: bool = False, maps: int = 1):
     """From a projection's row to attention's inputs.  src [T, W] holds q (H heads of head_dim), k (G heads of
     head_dim) and v (G heads of v_head_dim) at the column offsets `offsets` = (q, k, v); with `partials` (float32
     [S, T, W]) src is their sum.  Per head, in this order: root-mean-square norm of q and k with the weights
     q_norm / k_norm [head_dim] (None: none), rotation of the first rot_dims dimensions by the token's position from
     `table` (None: none), k times k_scale.  q goes to q_out [T, H, head_dim], k and v to the token's place in the
     cache (unless append is False).  norm_whole: the norm's mean square runs over all heads of q (of k) at once and the
-    weights are [H * head_dim] and [G * head_dim]."""
+    weights are [H * head_dim] and [G * head_dim].  norm_bare: q and k are divided by their root mean square per head
+    without a weight.  norm_last: the per-head norm follows the rotation.  maps > 1: every query head and every key head
+    is `maps` vectors of head_dim side by side, each normed and rotated like a head; q_out is [T, H * maps, head_dim]
+    and a cached key row holds maps * head_dim numbers."""
+    if norm_bare or norm_last or maps != 1:
+        return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
+                                     rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append, norm_whole=norm_whole,
+                                     norm_bare=norm_bare, norm_last=norm_last, maps=maps)
     if not norm_whole:
         return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
                                      rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append)
@@ -237,28 +260,41 @@ def retention_gate(o, src, gate_offset: int, out, n_head: int, v_head_dim: int, 
 
 def sigmoid_gate(y, gate, gate_off: int, group: int):
     """y[t, c] *= sigmoid(gate[t, gate_off + c // group]), in place: one gate per `group` columns of y [T, C]; gate
-    [T, Wg] of y's type."""
+    [T, Wg] of y's type or float32."""
     return kernels().sigmoid_gate(y, gate, gate_off, group)
 
 
-def moe_route(logits, correction, top: int, scale: float, idx, weights):
+def moe_route(logits, correction, top: int, scale: float, idx, weights, score: str = "sigmoid"):
     """Choice of experts.  logits float32 [T, >= E] (the first E columns count, E = len(correction)): s = sigmoid(logits);
     the `top` experts with the largest s + correction (lowest index on ties) go to idx int32 [T, top], and
-    weights float32 [T, top] = their s / (sum of the chosen s + 1e-20) * scale."""
-    return kernels().moe_route(logits, correction, top, scale, idx, weights)
+    weights float32 [T, top] = their s / (sum of the chosen s + 1e-20) * scale.  score 'softmax_top': the `top` largest
+    logits (+ correction) are chosen and weights = softmax over the chosen logits * scale."""
+    if score == "sigmoid":
+        return kernels().moe_route(logits, correction, top, scale, idx, weights)
+    return kernels().moe_route(logits, correction, top, scale, idx, weights, score=score)
 
 
-def moe_router(h, router, correction, top: int, scale: float, idx, weights):
-    """Router logits z = h router^T (32-bit) and `moe_route` on them.  h [T, D]; router [>= E, D] (rows beyond the E of
-    `correction` are padding).  A set of kernels may do both in one launch (`moe_router` returning True); otherwise the
-    product and the choice run one after the other."""
+def moe_router(h, router, correction, top: int, scale: float, idx, weights, score: str = "sigmoid", n_extra: int = 0):
+    """Router logits z = h router^T (32-bit) and `moe_route` on them.  h [T, D]; router [>= E + n_extra, D] (rows beyond
+    those are padding).  A set of kernels may do both in one launch (`moe_router` returning True); otherwise the
+    product and the choice run one after the other.  n_extra: that many rows behind the experts' are further 32-bit
+    products of the same input (a gate, say); returns (tensor float32 [T, >= n_extra], first column) where their logits
+    are, or None."""
     k = kernels()
     fused = getattr(k, "moe_router", None)
-    if fused is not None and fused(h, router, correction, top, scale, idx, weights):
-        return
+    E = correction.shape[0]
+    if fused is not None:
+        if score == "sigmoid" and n_extra == 0:
+            if fused(h, router, correction, top, scale, idx, weights):
+                return None
+        else:
+            extra = torch.empty(h.shape[0], n_extra, dtype=torch.float32, device=h.device) if n_extra else None
+            if fused(h, router, correction, top, scale, idx, weights, score=score, extra=extra):
+                return None if extra is None else (extra, 0)
     z = torch.empty(h.shape[0], router.shape[0], dtype=torch.float32, device=h.device)
     linear(h, router, z)
-    moe_route(z, correction, top, scale, idx, weights)
+    moe_route(z, correction, top, scale, idx, weights, score)
+    return (z, E) if n_extra else None
 
 
 def moe_experts(h, idx, weights, w13, w2, x, limit: float, alpha: float, shift: float = 1.0):
@@ -310,14 +346,23 @@ def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n
 
 def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int] = None, chunk: Optional[int] = None, sink=None, v_head_dim: Optional[int] = None,
-              values_in_keys: bool = False, bias=None, slopes=None):
+              values_in_keys: bool = False, bias=None, slopes=None, softcap: Optional[float] = None, keep_first: int = 0,
+              maps: int = 1, diff=None):
     """Causal grouped-query attention of q [T, H, d] over the cache (which
     already holds this step's keys and values); out [T, H*dv].  chunk: a query sees only the keys of its own block
     of `chunk` positions (counted from the sequence's first position).  sink (float32 [H]): exp(sink_h) joins the
     softmax denominator of head h, with no value.  v_head_dim: the values' head size if it differs from d.
     values_in_keys: a key's first v_head_dim numbers are also its value (the value pool is not read).
     bias (float32 [L, H]): bias[min(n, L - 1), h] is added to the scaled score of a key n positions back.
-    slopes (float32 [H]): slopes[h] * n is taken off it."""
+    slopes (float32 [H]): slopes[h] * n is taken off it.
+    softcap: the scaled score s becomes softcap * tanh(s / softcap).  keep_first (with a window): the sequence's first
+    keep_first positions stay visible beyond the window.  maps = 2 with diff = (lambda, eps, out_scale): q is [T, H * 2, d],
+    a cached key row holds two keys; each (query, key) pair is a softmax of its own over the same values, and the head's
+    output is (o_1 - lambda o_2) / sqrt(mean((o_1 - lambda o_2)^2) + eps) * out_scale."""
+    if softcap or keep_first or maps != 1:
+        return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
+                                   values_in_keys=values_in_keys, bias=bias, slopes=slopes, softcap=softcap, keep_first=keep_first,
+                                   maps=maps, diff=diff)
     if bias is not None or slopes is not None:
         return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
                                    values_in_keys=values_in_keys, bias=bias, slopes=slopes)

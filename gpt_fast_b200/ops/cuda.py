@@ -218,8 +218,9 @@ class CudaKernels:
         _need(x, torch.float32, name="norm input")
         if out is not None:
             R = out.shape[0]
-            _need(weight, shape=(D,), name="norm weight")
-            if not rms and bias is not None:
+            if weight is not None:
+                _need(weight, shape=(D,), name="norm weight")
+            if not rms and bias is not None and weight is not None:
                 _need(bias, weight.dtype, (D,), "norm bias")
             _need(out, shape=(R, D), name="norm output")
             if rows is not None:
@@ -246,7 +247,7 @@ class CudaKernels:
             return
         self._call("layernorm", "gfb_layernorm", _ptr(x), _ptr(y), c_int(S), c_long(T * D), _ptr(pw), _ptr(pb),
                    c_int(_dt(pw) if pw is not None else 0), c_float(peps), c_float(mult), _ptr(weight if out is not None else None),
-                   _ptr(bias if out is not None else None), c_int(_dt(weight) if out is not None else 0), c_float(eps),
+                   _ptr(bias if out is not None and weight is not None else None), c_int(_dt(weight) if out is not None and weight is not None else 0), c_float(eps),
                    _ptr(out), c_int(_dt(out) if out is not None else 0), _ptr(rows), c_int(R), c_int(D), c_int(1 if rms else 0),
                    _stream())
 
@@ -342,7 +343,7 @@ class CudaKernels:
             _fail(f"{need} numbers of state at column {state_off} do not fit rows of {tuple(state.shape)}")
         return c_void_p(state.data_ptr() + 4 * state_off), c_long(state.shape[1])
 
-    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True):
+    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True, in_bias=None):
         T = batch.n_tokens
         taps = weight.shape[1]
         _need(src, name="convolution input")
@@ -351,11 +352,34 @@ class CudaKernels:
         _need(weight, shape=(channels, taps), name="convolution weight")
         if bias is not None:
             _need(bias, weight.dtype, (channels,), "convolution bias")
+        if in_bias is not None:
+            _need(in_bias, weight.dtype, (channels,), "bias of the convolution's inputs")
         _need(out, torch.float32, (T, channels), "convolution output")
         sp, sld = self._state_args(state, state_off, (taps - 1) * channels)
         self._call("recurrent", "gfb_short_conv", _ptr(src), c_int(_dt(src)), c_int(src.shape[1]), c_int(col_off), c_int(channels),
-                   _ptr(weight), _ptr(bias), c_int(_dt(weight)), c_int(taps), sp, sld, _ptr(out), *self._batch_args(batch),
+                   _ptr(weight), _ptr(bias), _ptr(in_bias), c_int(_dt(weight)), c_int(taps), sp, sld, _ptr(out), *self._batch_args(batch),
                    c_int(1 if act else 0), _stream())
+
+    def rglru(self, u, w_a, w_i, b_a, b_i, lam, decay_scale, y_src, y_off, y_bias, state, state_off, out, batch):
+        T = batch.n_tokens
+        C = u.shape[1]
+        blocks, bw = w_a.shape[0], w_a.shape[1]
+        _need(u, torch.float32, (T, C), "recurrence input")
+        if blocks * bw != C:
+            _fail(f"gate matrices {tuple(w_a.shape)} do not cover {C} channels")
+        _need(w_a, shape=(blocks, bw, bw), name="recurrence gate matrices")
+        _need(w_i, w_a.dtype, (blocks, bw, bw), "input gate matrices")
+        for v, name in ((b_a, "recurrence gate bias"), (b_i, "input gate bias"), (lam, "decay parameter"), (y_bias, "gate branch bias")):
+            _need(v, b_a.dtype, (C,), name)
+        _need(y_src, name="gate branch")
+        if y_src.dim() != 2 or y_src.shape[0] != T or y_off + C > y_src.shape[1]:
+            _fail(f"{C} columns at {y_off} do not fit {tuple(y_src.shape)}")
+        _need(out, shape=(T, C), name="recurrence output")
+        sp, sld = self._state_args(state, state_off, C)
+        scratch = torch.empty(2, T, C, dtype=torch.float32, device=u.device)
+        self._call("recurrent", "gfb_rglru", _ptr(u), _ptr(w_a), _ptr(w_i), c_int(_dt(w_a)), _ptr(b_a), _ptr(b_i), _ptr(lam), _ptr(y_bias),
+                   c_int(_dt(b_a)), c_float(decay_scale), _ptr(y_src), c_int(_dt(y_src)), c_int(y_src.shape[1]), c_int(y_off), sp, sld,
+                   _ptr(out), c_int(_dt(out)), _ptr(scratch), *self._batch_args(batch), c_int(C), c_int(blocks), _stream())
 
     def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
                  n_state, n_groups):
@@ -411,8 +435,11 @@ class CudaKernels:
                    c_int(group), c_float(eps), c_int(1 if act == "sigmoid" else 0), c_int(1 if gate_first else 0), _stream())
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
-                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False):
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False,
+                    norm_bare=False, norm_last=False, maps=1):
         T = batch.n_tokens
+        if norm_whole and (norm_bare or norm_last or maps != 1):
+            _fail("a norm over the whole projection has weights, runs ahead of the rotation and knows one map per head")
         if partials is not None:
             W = partials.shape[2]
             _need(partials, torch.float32, (partials.shape[0], T, W), "partial sums of the projection")
@@ -422,10 +449,10 @@ class CudaKernels:
             _need(src, q_out.dtype, (T, W), "projection")
             source, n_part = src, 0
         q_off, k_off, v_off = offsets
-        ends = [q_off + n_head * head_dim] + ([k_off + n_kv * head_dim, v_off + n_kv * v_head_dim] if append else [])
+        ends = [q_off + n_head * maps * head_dim] + ([k_off + n_kv * maps * head_dim, v_off + n_kv * v_head_dim] if append else [])
         if max(ends) > W:
             _fail(f"q, k and v at {offsets} do not fit rows of {W}")
-        _need(q_out, shape=(T, n_head, head_dim), name="q_out")
+        _need(q_out, shape=(T, n_head * maps, head_dim), name="q_out")
         if table is not None:
             _need(table, torch.float32, name="rotary table")
             if table.shape[1] * 2 != rot_dims:
@@ -439,15 +466,16 @@ class CudaKernels:
             _fail("the q and k norm weights must have one type")
         if append:
             _need(kv.k_pool, q_out.dtype, name="key pool")
-            if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim) or tuple(kv.v_pool.shape[1:]) != (n_kv, kv.page_size, v_head_dim):
+            if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim * maps) or tuple(kv.v_pool.shape[1:]) != (n_kv, kv.page_size, v_head_dim):
                 _fail(f"cache pages are {tuple(kv.k_pool.shape[1:])} / {tuple(kv.v_pool.shape[1:])}, the layer needs "
-                      f"{(n_kv, kv.page_size, head_dim)} / {(n_kv, kv.page_size, v_head_dim)}")
+                      f"{(n_kv, kv.page_size, head_dim * maps)} / {(n_kv, kv.page_size, v_head_dim)}")
         self._call("qkv_prepare", "gfb_qkv_prepare", _ptr(source), c_int(n_part), c_int(W), c_int(q_off), c_int(k_off), c_int(v_off),
                    _ptr(q_out), c_int(_dt(q_out)), *self._kv_args(kv), *self._batch_args(batch), _ptr(table),
                    c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
                    c_int(_PAIRING[pairing]), _ptr(q_norm), _ptr(k_norm), c_int(w_dt), c_float(norm_eps), c_float(k_scale),
                    c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(v_head_dim), c_int(1 if append else 0),
-                   c_int(1 if norm_whole else 0), _ptr(batch.status), _stream())
+                   c_int((1 if norm_whole else 0) | (2 if norm_bare else 0) | (4 if norm_last else 0)), c_int(maps),
+                   _ptr(batch.status), _stream())
 
     def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
                   pairing="half", k_scale=1.0):
@@ -489,10 +517,12 @@ class CudaKernels:
     def sigmoid_gate(self, y, gate, gate_off, group):
         T, C = y.shape
         _need(y, name="gated tensor")
-        _need(gate, y.dtype, name="gate")
+        _need(gate, name="gate")
+        if gate.dtype not in (y.dtype, torch.float32):
+            _fail(f"a gate of {gate.dtype} on a tensor of {y.dtype}")
         if gate.dim() != 2 or gate.shape[0] != T or group < 1 or C % group or gate_off + C // group > gate.shape[1]:
             _fail(f"gates for groups of {group} of {C} columns at column {gate_off} do not fit {tuple(gate.shape)}")
-        self._call("elementwise", "gfb_sigmoid_gate", _ptr(y), _ptr(gate), c_int(_dt(y)), c_int(T), c_int(C), c_int(gate.shape[1]),
+        self._call("elementwise", "gfb_sigmoid_gate", _ptr(y), _ptr(gate), c_int(_dt(y)), c_int(_dt(gate)), c_int(T), c_int(C), c_int(gate.shape[1]),
                    c_int(gate_off), c_int(group), _stream())
 
     # -- mixture of experts ------------------------------------------------------------------
@@ -503,8 +533,12 @@ class CudaKernels:
     MOE_PAIR_ROWS_PER_EXPERT = 384     # (token, expert) pairs per expert from which the row tiles have 256 rows
     _EPI_GLU_CLAMP = 8
 
-    def moe_route(self, logits, correction, top, scale, idx, weights):
+    _ROUTE_SCORES = {"sigmoid": 0, "softmax_top": 1}
+
+    def moe_route(self, logits, correction, top, scale, idx, weights, score="sigmoid"):
         T = logits.shape[0]
+        if score not in self._ROUTE_SCORES:
+            _fail(f"unknown router score '{score}'")
         E = correction.shape[0]
         _need(logits, torch.float32, name="router logits")
         if logits.dim() != 2 or logits.shape[1] < E:
@@ -513,24 +547,30 @@ class CudaKernels:
         _need(idx, torch.int32, (T, top), "chosen experts")
         _need(weights, torch.float32, (T, top), "expert weights")
         self._call("moe", "gfb_moe_route", _ptr(logits), c_int(logits.shape[1]), _ptr(correction), c_int(_dt(correction)), c_int(E),
-                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), _stream())
+                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), c_int(self._ROUTE_SCORES[score]), _stream())
 
     MOE_ROUTER_FEW_TOKENS = 64         # up to this many tokens the router's product and its choice are one launch
 
-    def moe_router(self, h, router, correction, top, scale, idx, weights) -> bool:
+    def moe_router(self, h, router, correction, top, scale, idx, weights, score="sigmoid", extra=None) -> bool:
         T, D = h.shape
         E = correction.shape[0]
-        if T > self.MOE_ROUTER_FEW_TOKENS or (D + E) * 4 > 48 * 1024:
+        n_extra = 0 if extra is None else extra.shape[1]
+        if T > self.MOE_ROUTER_FEW_TOKENS or (D + E + n_extra) * 4 > 48 * 1024:
             return False
+        if score not in self._ROUTE_SCORES:
+            _fail(f"unknown router score '{score}'")
+        if extra is not None:
+            _need(extra, torch.float32, (T, n_extra), "logits of the further rows")
         _need(h, name="router input")
         _need(router, h.dtype, (router.shape[0], D), "router weights")
-        if router.shape[0] < E:
-            _fail(f"router weights {tuple(router.shape)} for {E} experts")
+        if router.shape[0] < E + n_extra:
+            _fail(f"router weights {tuple(router.shape)} for {E} experts and {n_extra} further rows")
         _need(correction, name="router correction")
         _need(idx, torch.int32, (T, top), "chosen experts")
         _need(weights, torch.float32, (T, top), "expert weights")
         self._call("moe", "gfb_moe_router", _ptr(h), _ptr(router), c_int(_dt(h)), _ptr(correction), c_int(_dt(correction)), c_int(E),
-                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), c_int(D), _stream())
+                   c_int(top), c_float(scale), _ptr(idx), _ptr(weights), c_int(T), c_int(D), c_int(self._ROUTE_SCORES[score]),
+                   c_int(n_extra), _ptr(extra), _stream())
         return True
 
     def moe_experts(self, h, idx, weights, w13, w2, x, limit, alpha, shift=1.0):
@@ -692,10 +732,14 @@ class CudaKernels:
 
     # -- attention ---------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
-                  values_in_keys=False, bias=None, slopes=None):
+                  values_in_keys=False, bias=None, slopes=None, softcap=None, keep_first=0, maps=1, diff=None):
         T = batch.n_tokens
         dv = v_head_dim or head_dim
-        _need(q, shape=(T, n_head, head_dim), name="q")
+        if maps not in (1, 2) or (maps == 2) != (diff is not None):
+            _fail("two score maps per head come with (lambda, eps, out_scale), one map without")
+        if keep_first and not window:
+            keep_first = 0                             # without a window every earlier position is visible anyway
+        _need(q, shape=(T, n_head * maps, head_dim), name="q")
         _need(out, q.dtype, (T, n_head * dv), "attention output")
         _need(kv.k_pool, q.dtype, name="key pool")
         if sink is not None:
@@ -705,8 +749,9 @@ class CudaKernels:
         if slopes is not None:
             _need(slopes, torch.float32, (n_head,), "distance slopes")
         biased = bias is not None or slopes is not None
-        plain = chunk is None and sink is None and not biased
-        if (values_in_keys and not biased and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
+        special = bool(softcap) or bool(keep_first) or maps != 1      # what only the generic kernel has
+        plain = chunk is None and sink is None and not biased and not special
+        if (values_in_keys and not biased and not special and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
                 and not window and head_dim % 16 == 0 and dv % 16 == 0 and dv <= 512 and dv < head_dim and kv.page_size % 32 == 0
                 and (64 + 2 * 32) * (head_dim + 8) * 2 <= 220 * 1024):
             # a latent that all heads share: the tensor-core kernel that fetches every cached row once per 64 (token, head)
@@ -723,7 +768,7 @@ class CudaKernels:
                               c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
                               c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), c_int(splits),
                               _ptr(scratch), _ptr(batch.status), _stream())
-        if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+        if (not values_in_keys and not special and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
                 and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256)) and (not biased or scale > 0)):
             # the tensor-core kernels; a block mask, a sink or a distance bias only at the head sizes they are built for
             return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink,
@@ -731,7 +776,9 @@ class CudaKernels:
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
                    c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), c_int(1 if values_in_keys else 0),
-                   _ptr(bias), c_int(bias.shape[0] if bias is not None else 0), _ptr(slopes), _ptr(batch.status), _stream())
+                   _ptr(bias), c_int(bias.shape[0] if bias is not None else 0), _ptr(slopes), c_float(softcap or 0.0),
+                   c_int(int(keep_first)), c_int(maps), c_float(diff[0] if diff else 0.0), c_float(diff[1] if diff else 0.0),
+                   c_float(diff[2] if diff else 1.0), _ptr(batch.status), _stream())
 
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)

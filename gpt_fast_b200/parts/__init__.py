@@ -87,4 +87,4 @@ def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):
 
 
 from . import norm, rope, attention, retention, feed_forward, block  # noqa: E402,F401  (register the built-in parts)
-from . import embedding, latent_attention, state_space, delta_rule, moe, mixer_sum  # noqa: E402,F401
+from . import embedding, latent_attention, state_space, delta_rule, moe, mixer_sum, diff_attention, rglru  # noqa: E402,F401

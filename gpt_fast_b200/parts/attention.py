@@ -28,6 +28,11 @@ Options beyond gpt-fast's attention, each off by default:
   gate             'head': head h's output times sigmoid(Wg h)_h, one gate per head; 'element': the concatenated heads times
                    sigmoid(Wg h), one gate per column (parameter wg)
   shared_kv        the layer has no key/value projections: it attends over the cache entry of another run with its own queries
+  qk_norm_weight   False: the per-head q/k norm has no weights
+  qk_norm_last     the per-head q/k norm follows the rotation instead of preceding it
+  values_are_keys  no value projection: a position's values are its keys as projected, ahead of norm and rotation
+  softcap          the scaled score s becomes softcap * tanh(s / softcap)
+  keep_first       with a window: the sequence's first `keep_first` positions stay visible to every later query
 With none of them the rotate-and-append kernel and the tensor-core attention kernels run; the others go through
 `ops.qkv_prepare` and the options of `ops.attention`."""
 import math
@@ -62,7 +67,8 @@ class Attention:
                  window: Optional[int] = None, scale: Optional[float] = None, v_head_dim: Optional[int] = None,
                  qk_norm_eps: Optional[float] = None, chunk: Optional[int] = None, sink: bool = False,
                  qk_norm_whole: bool = False, conv_taps: Optional[int] = None, distance_bias: Optional[dict] = None,
-                 gate: Optional[str] = None, shared_kv: bool = False):
+                 gate: Optional[str] = None, shared_kv: bool = False, qk_norm_weight: bool = True, qk_norm_last: bool = False,
+                 values_are_keys: bool = False, softcap: Optional[float] = None, keep_first: int = 0):
         if n_head % n_kv:
             raise ValueError(f"{n_head} query heads do not divide into {n_kv} key/value heads")
         if chunk is not None and chunk < 1:
@@ -76,6 +82,18 @@ class Attention:
         self.qk_norm_whole = bool(qk_norm_whole) and self.qk_norm_eps is not None
         self.conv_taps = int(conv_taps) if conv_taps else None
         self.gate, self.shared_kv = gate, bool(shared_kv)
+        self.qk_norm_weight, self.qk_norm_last = bool(qk_norm_weight), bool(qk_norm_last)
+        self.values_are_keys = bool(values_are_keys)
+        self.softcap = float(softcap) if softcap else None
+        self.keep_first = int(keep_first or 0)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a soft cap of {softcap} on the scores")
+        if self.keep_first < 0:
+            raise ValueError(f"{keep_first} kept first positions")
+        if self.values_are_keys and (self.v_head_dim != head_dim or self.shared_kv or conv_taps):
+            raise ValueError("values that are the projected keys have the keys' head size, a cache entry of their own and no convolution")
+        if self.qk_norm_whole and (not self.qk_norm_weight or self.qk_norm_last):
+            raise ValueError("a q/k norm over the whole projection has weights and precedes the rotation")
         if gate not in (None, "head", "element"):
             raise ValueError(f"an output gate is 'head' or 'element', not {gate!r}")
         self.distance_bias = dict(distance_bias) if distance_bias else None
@@ -86,14 +104,15 @@ class Attention:
                     raise ValueError("a distance table needs at least two rows and a far distance beyond its linear half")
             elif kind != "slopes":
                 raise ValueError(f"a distance bias is of kind 'slopes' or 'table', not {kind!r}")
-        extras = (self.qk_norm_whole or self.conv_taps or self.distance_bias is not None or gate is not None or self.shared_kv)
+        extras = (self.qk_norm_whole or self.conv_taps or self.distance_bias is not None or gate is not None or self.shared_kv
+                  or self.values_are_keys or self.softcap is not None or self.keep_first)
         self.plain = (position is not None and self.v_head_dim == head_dim and self.qk_norm_eps is None
                       and chunk is None and not self.has_sink and getattr(position, "head_dim", head_dim) == head_dim
                       and not extras)
         self.wqkv = self.wo = self.q_norm = self.k_norm = self.sink = None
         self.conv = self.bias_table = self.slopes = None
         # columns of the fused projection: q, then k and v (unless shared), then the gates
-        self.kv_cols = 0 if self.shared_kv else n_kv * (head_dim + self.v_head_dim)
+        self.kv_cols = 0 if self.shared_kv else n_kv * head_dim if self.values_are_keys else n_kv * (head_dim + self.v_head_dim)
         self.conv_channels = n_head * head_dim + self.kv_cols
         self.gate_cols = {None: 0, "head": n_head, "element": n_head * self.v_head_dim}[gate]
 
@@ -101,8 +120,10 @@ class Attention:
         H, G, d, dv, D = self.n_head, self.n_kv, self.head_dim, self.v_head_dim, self.dim
         specs = {"wq": ParamSpec((H * d, D)), "wo": ParamSpec((D, H * dv))}
         if not self.shared_kv:
-            specs.update(wk=ParamSpec((G * d, D)), wv=ParamSpec((G * dv, D)))
-        if self.qk_norm_eps is not None:
+            specs["wk"] = ParamSpec((G * d, D))
+            if not self.values_are_keys:
+                specs["wv"] = ParamSpec((G * dv, D))
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             specs["q_norm"] = ParamSpec(((H if self.qk_norm_whole else 1) * d,), "vector")
             if not self.shared_kv:
                 specs["k_norm"] = ParamSpec(((G if self.qk_norm_whole else 1) * d,), "vector")
@@ -121,12 +142,12 @@ class Attention:
     def load(self, tensors):
         # rows: q heads, then k heads, then v heads (gpt-fast model.py:184-189)
         self._stored = {k: v for k, v in tensors.items() if k not in ("wq", "wk", "wv", "wg", "wo")}
-        rows = [tensors["wq"]] + ([] if self.shared_kv else [tensors["wk"], tensors["wv"]])
+        rows = [tensors["wq"]] + ([] if self.shared_kv else [tensors["wk"]] if self.values_are_keys else [tensors["wk"], tensors["wv"]])
         if self.gate is not None:
             rows.append(tensors["wg"])
         self.wqkv = torch.cat(rows).contiguous() if self.plain or len(rows) == 3 and self.gate is None else _pad_rows(torch.cat(rows))
         self.wo = tensors["wo"]
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm = tensors["q_norm"]
             self.k_norm = None if self.shared_kv else tensors["k_norm"].to(tensors["q_norm"].dtype)
         if self.has_sink:
@@ -153,8 +174,9 @@ class Attention:
     def export(self):
         """The parameters as `load` received them (the way back from the fused layout)."""
         H, G, d, dv = self.n_head, self.n_kv, self.head_dim, self.v_head_dim
-        sizes = [H * d] + ([] if self.shared_kv else [G * d, G * dv]) + ([self.gate_cols] if self.gate is not None else [])
-        names = ["wq"] + ([] if self.shared_kv else ["wk", "wv"]) + (["wg"] if self.gate is not None else [])
+        kv = [] if self.shared_kv else [("wk", G * d)] if self.values_are_keys else [("wk", G * d), ("wv", G * dv)]
+        sizes = [H * d] + [n for _, n in kv] + ([self.gate_cols] if self.gate is not None else [])
+        names = ["wq"] + [k for k, _ in kv] + (["wg"] if self.gate is not None else [])
         out = dict(zip(names, self.wqkv[:sum(sizes)].split(sizes)), wo=self.wo)
         out.update({k: self._stored[k] for k in self.param_specs() if k not in out})
         return out
@@ -190,7 +212,12 @@ class Attention:
                 ops.short_conv(qkv, 0, C, self.conv, None, state, 0, conv, batch, act=False)
                 src, partials = None, conv.view(1, T, C)                    # the 32-bit rows, taken as a sum of one part
             kw = {"norm_whole": True} if self.qk_norm_whole else {}
-            ops.qkv_prepare(src, partials, (0, H * d, (H + G) * d), q, view.kv, batch, H, G, d, dv,
+            if self.qk_norm_eps is not None and not self.qk_norm_weight:
+                kw["norm_bare"] = True
+            if self.qk_norm_last:
+                kw["norm_last"] = True
+            # values that are the keys as projected: the value columns of the row are its key columns
+            ops.qkv_prepare(src, partials, (0, H * d, H * d if self.values_are_keys else (H + G) * d), q, view.kv, batch, H, G, d, dv,
                             table=None if pos is None else pos.table, rot_dims=0 if pos is None else pos.head_dim,
                             pairing="half" if pos is None else pos.pairing, q_norm=self.q_norm, k_norm=self.k_norm,
                             norm_eps=self.qk_norm_eps or 0.0, append=append, **kw)
@@ -199,6 +226,10 @@ class Attention:
                 kw["bias"] = self.bias_table
             if self.slopes is not None:
                 kw["slopes"] = self.slopes
+            if self.softcap is not None:
+                kw["softcap"] = self.softcap
+            if self.keep_first and self.window:
+                kw["keep_first"] = self.keep_first
             ops.attention(q, view.kv, batch, y, H, G, d, self.scale, self.window, self.chunk, self.sink, dv, **kw)
             if self.gate is not None:
                 ops.sigmoid_gate(y, qkv, H * d + self.kv_cols, dv if self.gate == "head" else 1)

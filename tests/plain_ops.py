@@ -81,15 +81,18 @@ class PlainOps:
         y.copy_((y.double() * g).to(y.dtype))
 
     # -- mixture of experts ---------------------------------------------------------------------
-    def moe_route(self, logits, correction, top, scale, idx, weights):
+    def moe_route(self, logits, correction, top, scale, idx, weights, score="sigmoid"):
         E = correction.shape[0]
-        s = torch.sigmoid(logits[:, :E].float())
+        s = torch.sigmoid(logits[:, :E].float()) if score == "sigmoid" else logits[:, :E].float()
         choice = s + correction.float()
         for t in range(s.shape[0]):
             order = sorted(range(E), key=lambda e: (-float(choice[t, e]), e))[:top]
             picked = s[t, order]
             idx[t] = torch.tensor(order, dtype=idx.dtype)
-            weights[t] = picked / (picked.sum() + 1e-20) * scale
+            if score == "sigmoid":
+                weights[t] = picked / (picked.sum() + 1e-20) * scale
+            else:
+                weights[t] = torch.softmax(picked.double(), -1).float() * scale
 
     def moe_experts(self, h, idx, weights, w13, w2, x, limit, alpha, shift=1.0):
         hd = h.double()
@@ -115,6 +118,8 @@ class PlainOps:
     def layernorm(self, x, weight, bias, eps, out, rows=None, branch=None, rms=False):
         def norm(v, w, b, e):
             v = v.double()
+            if w is None:
+                return v
             if rms:
                 return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + e) * w.double()
             dev = v - v.mean(-1, keepdim=True)
@@ -178,10 +183,12 @@ class PlainOps:
             out[:, out_off + h * out_stride:out_off + h * out_stride + n] = y.to(out.dtype)
 
     # -- recurrent mixers -----------------------------------------------------------------------
-    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True):
+    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True, in_bias=None):
         taps, C = weight.shape[1], channels
         w = weight.double()
         x = src[:, col_off:col_off + C].double()
+        if in_bias is not None:
+            x = x + in_bias.double()
         cu = batch.cu_seqlens.tolist()
         for s in range(batch.n_seqs):
             slot = int(batch.slots[s])
@@ -196,6 +203,25 @@ class PlainOps:
             out[cu[s]:cu[s + 1]] = (y / (1 + torch.exp(-y)) if act else y).float()
             if taps > 1:                                           # one tap carries nothing
                 state[slot, state_off:state_off + (taps - 1) * C] = seq[n:].reshape(-1).float()
+
+    def rglru(self, u, w_a, w_i, b_a, b_i, lam, decay_scale, y_src, y_off, y_bias, state, state_off, out, batch):
+        T, C = u.shape
+        blocks, bw = w_a.shape[0], w_a.shape[1]
+        ub = u.double().view(T, blocks, bw)
+        r = torch.sigmoid(torch.einsum("tbi,bio->tbo", ub, w_a.double()).reshape(T, C) + b_a.double())
+        g = torch.sigmoid(torch.einsum("tbi,bio->tbo", ub, w_i.double()).reshape(T, C) + b_i.double())
+        log_a = -decay_scale * r * torch.nn.functional.softplus(lam.double())
+        a, b = torch.exp(log_a), torch.sqrt(-torch.expm1(2 * log_a)) * g * u.double()
+        z = y_src[:, y_off:y_off + C].double() + y_bias.double()
+        gate = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+        cu = batch.cu_seqlens.tolist()
+        for s in range(batch.n_seqs):
+            slot = int(batch.slots[s])
+            S = state[slot, state_off:state_off + C].double()
+            for t in range(cu[s], cu[s + 1]):
+                S = a[t] * S + b[t]
+                out[t] = (S * gate[t]).to(out.dtype)
+            state[slot, state_off:state_off + C] = S.float()
 
     def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
                  n_state, n_groups):
@@ -268,15 +294,16 @@ class PlainOps:
         return out
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
-                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False):
-        H, G, d, dv = n_head, n_kv, head_dim, v_head_dim
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False,
+                    norm_bare=False, norm_last=False, maps=1):
+        H, G, d, dv = n_head * maps, n_kv * maps, head_dim, v_head_dim
         T = batch.n_tokens
         x = (partials.double().sum(0) if partials is not None else src.double())
         qo, ko, vo = offsets
         q = x[:, qo:qo + H * d].reshape(T, H, d)
         if append:
             k = x[:, ko:ko + G * d].reshape(T, G, d)
-            v = x[:, vo:vo + G * dv].reshape(T, G, dv)
+            v = x[:, vo:vo + n_kv * dv].reshape(T, n_kv, dv)
         else:                                                  # only q is made: the row may hold no keys or values at all
             k, k_norm = x.new_zeros(T, G, d), None
         pos, slots = token_positions(batch)
@@ -286,20 +313,26 @@ class PlainOps:
             if k_norm is not None:
                 k = k * torch.rsqrt((k * k).mean((-2, -1), keepdim=True) + norm_eps) * k_norm.double().view(G, d)
             q_norm = k_norm = None
-        if q_norm is not None:
-            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps) * q_norm.double()
-        if k_norm is not None:
-            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + norm_eps) * k_norm.double()
+
+        def head_norm(v, w):
+            if w is None and not norm_bare:
+                return v
+            v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + norm_eps)
+            return v if w is None else v * w.double()
+        if not norm_last and not norm_whole:
+            q, k = head_norm(q, q_norm), head_norm(k, k_norm) if append else k
         if table is not None:
             cs = table[pos].double()
             q, k = self._rotate_front(q, cs, rot_dims, pairing), self._rotate_front(k, cs, rot_dims, pairing)
+        if norm_last and not norm_whole:
+            q, k = head_norm(q, q_norm), head_norm(k, k_norm) if append else k
         q_out.copy_(q.to(q_out.dtype))
         if append:
             page = kv.page_table.long()[slots, pos // kv.page_size]
             if int(page.min()) < 0:
                 raise IndexError("token lands on a page the slot does not hold")
             off = pos % kv.page_size
-            kv.k_pool[page, :, off] = (k * k_scale).to(kv.k_pool.dtype)
+            kv.k_pool[page, :, off] = (k * k_scale).reshape(T, n_kv, maps * d).to(kv.k_pool.dtype)
             kv.v_pool[page, :, off] = v.to(kv.v_pool.dtype)
 
     def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
@@ -411,7 +444,7 @@ class PlainOps:
 
     # -- attention -----------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
-                  values_in_keys=False, bias=None, slopes=None):
+                  values_in_keys=False, bias=None, slopes=None, softcap=None, keep_first=0, maps=1, diff=None):
         H, G, d = n_head, n_kv, head_dim
         dv = v_head_dim or head_dim
         pos, slots = token_positions(batch)
@@ -423,6 +456,8 @@ class PlainOps:
             if chunk:
                 lo = max(lo, p // chunk * chunk)
             j = torch.arange(lo, p + 1, device=q.device)
+            if keep_first and window and lo > 0:
+                j = torch.cat([torch.arange(0, min(keep_first, lo), device=q.device), j])
             pages = kv.page_table.long()[slot, j // kv.page_size]
             if int(pages.min()) < 0:
                 raise IndexError("attention reads a page the slot does not hold")
@@ -430,11 +465,22 @@ class PlainOps:
             v = k[..., :dv] if values_in_keys else kv.v_pool[pages, :, j % kv.page_size].double()
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
+            if maps == 2:
+                # two softmax maps per head over the same values; their difference, normed per head and scaled
+                lam, eps, out_scale = diff
+                qm, km = q[t].double().view(H, 2, d), k.view(-1, H, 2, d)
+                o = [torch.einsum("hn,nhd->hd", torch.softmax(torch.einsum("hd,nhd->hn", qm[:, m], km[:, :, m]) * scale, -1), v)
+                     for m in range(2)]
+                o = o[0] - lam * o[1]
+                res[t] = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * out_scale
+                continue
             s = torch.einsum("hd,nhd->hn", q[t].double(), k) * scale
             if bias is not None:
                 s = s + bias.double()[(p - j).clamp(max=bias.shape[0] - 1)].T
             if slopes is not None:
                 s = s - slopes.double()[:, None] * (p - j).double()[None, :]
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             if sink is not None:
                 w = torch.softmax(torch.cat([s, sink.double()[:, None]], dim=-1), -1)[:, :-1]
             else:
