@@ -409,6 +409,11 @@ def design_bench(a, design):
               # reads about as many weights per token as 4 of Lomusun's experts of 1792 do
               "lomusun": [("lomusun-1b", a.layers, "lasezen", lambda cfg: dict(config_from_name("lasezen-1b"),
                                                                                layers=config_from_name("lasezen-1b")["layers"][:len(cfg["layers"])]))]}
+    # beside Tapupel: the library's other design of windowed attention, a recurrent mixer, readers of another layer's keys and
+    # routed experts, at the same width, depth, heads, head size, window and vocabulary; both read four experts of 1792 per
+    # token (Tapupel: three routed and the shared one)
+    tables["tapupel"] = [("tapupel-1b", a.layers, "lomusun", lambda cfg: dict(config_from_name("lomusun-1b"),
+                                                                             layers=config_from_name("lomusun-1b")["layers"][:len(cfg["layers"])]))]
     if design not in tables:
         print(f"bench.py: no size table for design '{design}'")
         return 2
@@ -460,7 +465,7 @@ def main():
     ap.add_argument("--skip-configs", action="store_true", help="leave out the Llama-3.2-3B and Llama-2-13B sizes")
     ap.add_argument("--skip-shares", action="store_true", help="leave out the per-kernel shares")
     ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode of another design "
-                    "(lasezen, gikepel, lomusun) at layer sizes of a real model, beside the library's closest other model at equal size")
+                    "(lasezen, gikepel, lomusun, tapupel) at layer sizes of a real model, beside the library's closest other model at equal size")
     ap.add_argument("--design-model", default=None, help=argparse.SUPPRESS)       # one model of --design, run as a child process
     ap.add_argument("--design-label", default="model", help=argparse.SUPPRESS)
     ap.add_argument("--prefill-lengths", default=None, help="with --design: prompt lengths of the prefill rows (default 512,2048,8192)")

@@ -61,6 +61,7 @@ class ModelSpec:
     embed_scale: Optional[float] = None   # factor on the embedding rows (None: 1)
     logit_cap: Optional[float] = None     # soft cap on the logits, cap * tanh(logits / cap) (None: none)
     embedding: Optional[PartSpec] = None  # what is added to the token embedding (a part of `parts.EMBEDDINGS`; None: nothing)
+    launch_overlap: bool = True           # kernels of a step may start while their predecessor drains; False: strictly in turn
 
     def validate(self) -> None:
         if self.logit_cap is not None and not self.logit_cap > 0:

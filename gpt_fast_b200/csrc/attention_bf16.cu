@@ -307,6 +307,10 @@ struct RopeSource {
     const float* bias;        // [bias_len][H], 32-bit: row min(n, bias_len - 1) is added
     int bias_len;
     const float* slopes;      // [H], 32-bit: slopes[h] * n is taken off
+    // two more (off when zero; only with queries that are ready, SRC_Q):
+    int keep_first;           // with a window: the sequence's first keep_first positions stay visible.  The grid's LAST slice
+                              // takes them (the pages ahead of the window that hold them); the others share the window
+    float softcap;            // the scaled score s becomes softcap * tanh(s / softcap)
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
@@ -408,6 +412,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int q_off = one_each ? 0 : t - b.cu_seqlens[s];
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
     int pos, lo, first_page, last_page, per, p0, p1;
+    int seen_lo, seen_hi;                        // the positions this block's mask lets through
     auto plan = [&](int len) {
         pos = len + q_off;
         lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -415,9 +420,20 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         first_page = lo / PAGE;
         last_page = pos / PAGE;
         const int n_pages = last_page - first_page + 1;
-        per = (n_pages + splits - 1) / splits;
-        p0 = first_page + z * per;
-        p1 = min(last_page + 1, p0 + per);
+        const int window_slices = rs.keep_first > 0 ? splits - 1 : splits;
+        per = (n_pages + window_slices - 1) / window_slices;
+        if (rs.keep_first > 0 && z == splits - 1) {
+            // the slice of the kept first positions: those ahead of the window (the window's own slices see the rest)
+            seen_lo = 0;
+            seen_hi = min(rs.keep_first, lo) - 1;
+            p0 = 0;
+            p1 = (seen_hi + PAGE) / PAGE;        // no such position: no page
+        } else {
+            seen_lo = lo;
+            seen_hi = pos;
+            p0 = first_page + z * per;
+            p1 = min(last_page + 1, p0 + per);
+        }
     };
     bool bad_page = false;                       // uniform over the block
     int bad_index = 0;
@@ -664,8 +680,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 int j = p * PAGE + warp * 16 + n * 8 + 2 * t4 + e;
-                const bool seen = j >= lo && j <= pos;
+                const bool seen = j >= seen_lo && j <= seen_hi;
                 float x = seen ? sc[n][e] * scale_log2e : -INFINITY;
+                if (seen && rs.softcap > 0.f) {
+                    // cap tanh(s / cap) in units of log2: tanh(y) = 1 - 2 / (e^2y + 1), with x = s log2(e)
+                    const float cap2 = rs.softcap * 1.4426950408889634f;
+                    x = cap2 - __fdividef(2.f * cap2, exp2f(2.f * x / rs.softcap) + 1.f);
+                }
                 if (seen && gq < rep) {
                     const int head = g * rep + gq;
                     if (rs.bias != nullptr) x = fmaf(rs.bias[(size_t)min(pos - j, rs.bias_len - 1) * H + head], 1.4426950408889634f, x);
@@ -916,12 +937,35 @@ GFB_API int gfb_attn_decode_masked(const void* q, void* out, void* k_pool, void*
 // The same with a bias on the scaled score that depends on the head and the distance n = query position - key position:
 // `bias` (float32 [bias_len][H] or null: row min(n, bias_len - 1) is added) and `slopes` (float32 [H] or null:
 // slopes[h] * n is taken off).  head_dim 64 or 128 only.
+// ... and with a soft cap on the scaled score and kept first positions (head_dim 64 or 128).  With keep_first > 0 (and a
+// window) `splits` counts one slice more than the window is cut into, at least 2: the last one takes the kept positions.
+GFB_API int gfb_attn_decode_capped(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, const float* bias, int bias_len, const float* slopes, float softcap,
+                                   int keep_first, int splits, float* scratch, int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_decode_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                    int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                    const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                    int chunk, const float* sink, const float* bias, int bias_len, const float* slopes, int splits,
                                    float* scratch, int* status, cudaStream_t stream) {
+    return gfb_attn_decode_capped(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots, lengths,
+                                  n_seqs, n_tokens, H, G, d, scale, window, chunk, sink, bias, bias_len, slopes, 0.f, 0, splits, scratch,
+                                  status, stream);
+}
+
+GFB_API int gfb_attn_decode_capped(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, const float* bias, int bias_len, const float* slopes, float softcap,
+                                   int keep_first, int splits, float* scratch, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (softcap < 0.f || keep_first < 0) return gfb_fail("gfb_attn_decode: a soft cap of %f, %d kept first positions", softcap, keep_first);
+    if (keep_first > 0 && (window <= 0 || chunk > 0)) return gfb_fail("gfb_attn_decode: kept first positions go with a window");
+    if ((softcap > 0.f || keep_first > 0) && d != 64 && d != 128)
+        return gfb_fail("gfb_attn_decode: a soft cap or kept first positions need head_dim 64 or 128, got %d", d);
+    if (keep_first > 0 && splits < 2) return gfb_fail("gfb_attn_decode: kept first positions take a slice of their own (%d slices)", splits);
     if ((bias != nullptr || slopes != nullptr) && d != 64 && d != 128)
         return gfb_fail("gfb_attn_decode_biased: a distance bias needs head_dim 64 or 128, got %d", d);
     if (bias != nullptr && bias_len < 1) return gfb_fail("gfb_attn_decode_biased: a distance table of %d rows", bias_len);
@@ -953,6 +997,8 @@ GFB_API int gfb_attn_decode_biased(const void* q, void* out, void* k_pool, void*
         rs.bias = bias;
         rs.bias_len = bias_len;
         rs.slopes = slopes;
+        rs.keep_first = keep_first;
+        rs.softcap = softcap;
         e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, rs, 0);
         if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     } else {

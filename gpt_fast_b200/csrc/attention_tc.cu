@@ -363,7 +363,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
                        GfbBatch b, int H, int G, float scale_log2e, int window, int chunk, const float* __restrict__ sink,
-                       DistanceBias db, int n_x, int* status) {
+                       DistanceBias db, int n_x, int* status, float cap_raw, float* __restrict__ lse_out) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 0) { prefetch_map(&map_q); prefetch_map(&map_k); prefetch_map(&map_v); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -588,6 +588,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 } else if (db.table != nullptr || db.slopes != nullptr)
                     add_distance_bias<2>(v, db, H, t.g * rep + (r - tq * rep), row_pos, key0);
+                if (cap_raw > 0.f) {
+                    // a soft cap on the scaled score, in units of the raw score: cap tanh(s / cap), tanh(x) = 1 - 2 / (e^2x + 1)
+                    const float two_over = 2.8853900817779268f / cap_raw;    // 2 log2(e) / cap
+#pragma unroll
+                    for (int c = 0; c < 2; c++)
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const float e = fast_exp2(v[c][i] * two_over);
+                            v[c][i] = cap_raw - __fdividef(2.f * cap_raw, e + 1.f);
+                        }
+                }
                 if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
 #pragma unroll
                     for (int c = 0; c < 2; c++)
@@ -682,6 +693,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // a sink: one more term of the sum under the row's reference maximum, with no value behind it
             if (sink != nullptr && m_run != -INFINITY) l_run += fast_exp2(sink[head] * 1.4426950408889634f - m_run * scale_log2e);
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            // the row's log-sum-exp in units of log2, for a caller that merges further keys into the row afterwards
+            if (lse_out != nullptr && row_ok && half == 0)
+                lse_out[(size_t)(t.t_first + t.tq0 + tq) * H + head] = l_run > 0.f ? fmaf(m_run, scale_log2e, log2f(l_run)) : -INFINITY;
             __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * DH + half * (DH / 2);   // each warp stores its half of the columns
 #pragma unroll 1
             for (int c = 0; c < NH; c++) {
@@ -1094,15 +1108,99 @@ GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, v
                                       max_blocks, status, stream);
 }
 
+// Kept first positions: behind the windowed attention, every query whose window no longer reaches the sequence's start takes
+// the first positions it does not see (j < min(keep_first, first key of its window)) into its row: with the row's log-sum-exp
+// L (log2 units) from the attention kernel and x_j = log2(e) cap(scale q.k_j),
+//     M = max(L, max_j x_j),  w = 2^(L - M),  out <- (w out + sum_j 2^(x_j - M) v_j) / (w + sum_j 2^(x_j - M)).
+// One block per (token, head); the kept positions are few.
+template <int DH>
+__global__ void __launch_bounds__(DH)
+attn_kept_merge_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const float* __restrict__ lse,
+                       const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                       const int* __restrict__ page_table, int max_pages, int n_pages, GfbBatch b, int H, int G, float scale,
+                       float softcap, int window, int keep_first, int* status) {
+    __shared__ float red[DH / 32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
+    const int lo = pos - window + 1;
+    const int kept = min(keep_first, lo);
+    if (kept <= 0) return;
+    const int g = h / (H / G);
+    const float qi = __bfloat162float(q[((size_t)t * H + h) * DH + i]);
+    const size_t at = ((size_t)t * H + h) * DH + i;
+    float m = lse[(size_t)t * H + h], den = 1.f, acc = __bfloat162float(out[at]);    // in units of 2^m
+    if (m == -INFINITY) { den = 0.f; acc = 0.f; }
+    for (int j = 0; j < kept; j++) {
+        const int pi = j / PAGE;
+        const int page = pi < max_pages ? page_table[(size_t)slot * max_pages + pi] : -1;
+        if (page < 0 || page >= n_pages) {
+            if (i == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi);
+            return;
+        }
+        const size_t row = (((size_t)page * G + g) * PAGE + (j - pi * PAGE)) * DH + i;
+        float dot = qi * __bfloat162float(k_pool[row]);
+        dot = gfb_warp_sum(dot);
+        __syncthreads();                                       // red is free again
+        if ((i & 31) == 0) red[i >> 5] = dot;
+        __syncthreads();
+        float sc = 0.f;
+#pragma unroll
+        for (int w = 0; w < DH / 32; w++) sc += red[w];
+        sc *= scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+        const float x = sc * 1.4426950408889634f;
+        const float m_new = fmaxf(m, x);
+        const float down = m == -INFINITY ? 0.f : exp2f(m - m_new), p = exp2f(x - m_new);
+        den = den * down + p;
+        acc = acc * down + p * __bfloat162float(v_pool[row]);
+        m = m_new;
+    }
+    out[at] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+}
+
 // The same with a bias by head and distance in units of the raw score (the bias divided by `scale`): `bias` null or
 // float32 [4][H][bias_len], the four moved copies of the per-head array that `DistanceBias` describes, with distance 0 at
 // entry bias_top; `slopes` null or float32 [H].
+// ... and with a soft cap on the scaled score (softcap > 0: cap tanh(s / cap)) and kept first positions (keep_first > 0, with a
+// window: the sequence's first keep_first positions stay visible to every later query).  Both run in the one-tile kernel; the
+// kept positions are merged into the rows by a second kernel, for which the first leaves every row's log-sum-exp in `lse`
+// (float32 [n_tokens * H], the caller's scratch).
+GFB_API int gfb_attn_prefill_tc_capped(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, const float* bias, int bias_len, int bias_top,
+                                       const float* slopes, float softcap, int keep_first, float* lse, int tiles, int max_blocks,
+                                       int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                        int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                        const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                        int chunk, const float* sink, const float* bias, int bias_len, int bias_top,
                                        const float* slopes, int tiles, int max_blocks, int* status, cudaStream_t stream) {
+    return gfb_attn_prefill_tc_capped(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                                      lengths, n_seqs, n_tokens, H, G, d, scale, window, chunk, sink, bias, bias_len, bias_top, slopes,
+                                      0.f, 0, nullptr, tiles, max_blocks, status, stream);
+}
+
+GFB_API int gfb_attn_prefill_tc_capped(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, const float* bias, int bias_len, int bias_top,
+                                       const float* slopes, float softcap, int keep_first, float* lse, int tiles, int max_blocks,
+                                       int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (softcap < 0.f || keep_first < 0 || ((softcap > 0.f || keep_first > 0) && !(scale > 0.f)))
+        return gfb_fail("gfb_attn_prefill_tc: a soft cap of %f, %d kept first positions, a scale of %f", softcap, keep_first, scale);
+    if (keep_first > 0 && (window <= 0 || chunk > 0)) keep_first = 0;          // no window: every earlier position is seen anyway
+    if (keep_first > 0 && (lse == nullptr || sink != nullptr || bias != nullptr || slopes != nullptr))
+        return gfb_fail("gfb_attn_prefill_tc: kept first positions need scratch for the rows' log-sum-exp and go without a sink or a distance bias");
+    if (keep_first == 0) lse = nullptr;
+    if (softcap > 0.f || keep_first > 0) tiles = 1;
+    const float cap_raw = softcap > 0.f ? softcap / scale : 0.f;
     if (bias != nullptr && (bias_len % 4 || bias_len < 128 + 4 + 384 || bias_top < 127 || bias_top + 384 >= bias_len
                             || (reinterpret_cast<uintptr_t>(bias) & 15)))
         return gfb_fail("gfb_attn_prefill_tc: a distance array of %d entries with distance 0 at %d (128 far entries ahead of the table, "
@@ -1191,10 +1289,24 @@ GFB_API int gfb_attn_prefill_tc_biased(const void* q, void* out, void* k_pool, v
         if (blocks > cap) blocks = cap;
         if (d == 128)
             e = gfb_launch(attn_prefill_tc_kernel<128>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status, cap_raw, lse);
         else
             e = gfb_launch(attn_prefill_tc_kernel<64>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, db, n_x, status, cap_raw, lse);
     }
-    return gfb_check(e, "gfb_attn_prefill_tc");
+    if (gfb_check(e, "gfb_attn_prefill_tc")) return 1;
+    if (keep_first > 0) {
+        if (H > 65535) return gfb_fail("gfb_attn_prefill_tc: %d heads exceed the grid limit", H);
+        const dim3 grid(n_tokens, H);
+        if (d == 128)
+            e = gfb_launch(attn_kept_merge_kernel<128>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const float*)lse,
+                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages, n_pages, b, H, G, scale, softcap,
+                           window, keep_first, status);
+        else
+            e = gfb_launch(attn_kept_merge_kernel<64>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const float*)lse,
+                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages, n_pages, b, H, G, scale, softcap,
+                           window, keep_first, status);
+        return gfb_check(e, "gfb_attn_prefill_tc (kept first positions)");
+    }
+    return 0;
 }

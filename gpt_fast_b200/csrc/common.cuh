@@ -52,8 +52,13 @@ static inline int gfb_check_launch(const char* what) {
     return 0;
 }
 
+// 1: kernels are launched so that they may start while their predecessor drains (see below); 0: one after the other;
+// -1: not asked yet (the environment decides).  One copy per library; `gfb_set_overlap` sets it.
+static int gfb_pdl_state = -1;
+
 #define GFB_DEFINE_LAST_ERROR() \
-    GFB_API const char* gfb_last_error() { return gfb_error_text; }
+    GFB_API const char* gfb_last_error() { return gfb_error_text; } \
+    GFB_API void gfb_set_overlap(int on) { gfb_pdl_state = on ? -1 : 0; }
 
 // ---- launches with programmatic dependent launch -----------------------------------
 // Every kernel of the library is launched with the attribute that lets it start
@@ -65,17 +70,17 @@ static inline int gfb_check_launch(const char* what) {
 // successor to become resident.  Because every block of every kernel executes
 // the wait before it touches anything an earlier kernel wrote, completion stays
 // ordered along the whole chain.  GFB_NO_PDL=1 in the environment turns the
-// attribute off (the two instructions are then no-ops).
+// attribute off (the two instructions are then no-ops), and so does `gfb_set_overlap(0)` for the launches of one
+// library until `gfb_set_overlap(1)`.
 __device__ __forceinline__ void gfb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void gfb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 static inline bool gfb_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
+    if (gfb_pdl_state < 0) {
         const char* e = getenv("GFB_NO_PDL");
-        on = (e != nullptr && e[0] == '1') ? 0 : 1;
+        gfb_pdl_state = (e != nullptr && e[0] == '1') ? 0 : 1;
     }
-    return on == 1;
+    return gfb_pdl_state == 1;
 }
 
 template <typename... KArgs, typename... Args>

@@ -1,7 +1,8 @@
 // Unary activations over a tensor, in place or to another tensor of the same type: the exact
 // (erf) GELU, the tanh form of GELU, SiLU, and the square of ReLU.  Arithmetic is 32-bit.  Products apply the same
 // functions in their epilogue where they can; this kernel serves the shapes that cannot.
-// Also a sigmoid gate on the columns of a tensor, one gate per group of columns (a head, or a single column).
+// Also a sigmoid gate on the columns of a tensor, one gate per group of columns (a head, or a single column), and the
+// last step of differential attention: the difference of a head's two maps, normed over the head.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -60,4 +61,38 @@ GFB_API int gfb_sigmoid_gate(void* y, const void* gate, int dt, int gate_dt, int
     else if (dt == GFB_F32 && gate_dt == GFB_F32) e = gfb_launch(sigmoid_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)y, (const float*)gate, C, ld_gate, gate_off, group, n);
     else return gfb_fail("gfb_sigmoid_gate: unsupported types %d and %d", dt, gate_dt);
     return gfb_check(e, "gfb_sigmoid_gate");
+}
+
+// a [T, H, 2, dv]: the outputs of a head's two score maps; out[t, h, :] = o / sqrt(mean(o^2) + eps) * out_scale with
+// o = a[t, h, 0, :] - lambda a[t, h, 1, :].  A warp per (token, head); 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const T* __restrict__ a, T* __restrict__ out, long items, int dv, float lambda, float eps, float out_scale) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const T* a1 = a + (size_t)item * 2 * dv;
+    const T* a2 = a1 + dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) {
+        const float o = gfb_to_f32(a1[i]) - lambda * gfb_to_f32(a2[i]);
+        ss = fmaf(o, o, ss);
+    }
+    ss = gfb_warp_sum(ss);
+    const float f = out_scale / sqrtf(ss / (float)dv + eps);
+    T* dst = out + (size_t)item * dv;
+    for (int i = lane; i < dv; i += 32) dst[i] = gfb_from_f32<T>((gfb_to_f32(a1[i]) - lambda * gfb_to_f32(a2[i])) * f);
+}
+
+GFB_API int gfb_diff_combine(const void* a, void* out, int dt, int T, int H, int dv, float lambda, float eps, float out_scale, cudaStream_t stream) {
+    const long items = (long)T * H;
+    if (items <= 0 || dv <= 0) return 0;
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    cudaError_t e;
+    if (dt == GFB_BF16) e = gfb_launch(diff_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, (const __nv_bfloat16*)a, (__nv_bfloat16*)out, items, dv, lambda, eps, out_scale);
+    else if (dt == GFB_F32) e = gfb_launch(diff_combine_kernel<float>, dim3(blocks), dim3(128), 0, stream, (const float*)a, (float*)out, items, dv, lambda, eps, out_scale);
+    else return gfb_fail("gfb_diff_combine: unknown type %d", dt);
+    return gfb_check(e, "gfb_diff_combine");
 }

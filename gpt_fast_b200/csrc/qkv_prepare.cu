@@ -19,7 +19,7 @@
 GFB_DEFINE_LAST_ERROR()
 
 constexpr int WARPS = 4;
-enum { NORM_WHOLE = 1, NORM_BARE = 2, NORM_LAST = 4 };
+enum { NORM_WHOLE = 1, NORM_BARE = 2, NORM_LAST = 4, Q_SPREAD = 8 };
 
 __device__ __forceinline__ float ld_w(const void* p, int dt, int i) {
     return dt == GFB_BF16 ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
@@ -49,7 +49,9 @@ qkv_prepare_kernel(const void* __restrict__ src, int S, size_t slice, int width,
     bool ok = pos >= 0 && (table == nullptr || pos < table_len);
     T* dst = nullptr;
     if (is_q) {
-        dst = q_out + ((size_t)t * H + head) * dk;
+        // Q_SPREAD: q_out rows are maps * dk wide and map m of a head sits at columns m * dk .. of its own row (the rest stays
+        // as the caller left it: zeros), so that against a cached row of `maps` keys side by side it meets its own key only
+        dst = (norm_opts & Q_SPREAD) ? q_out + (((size_t)t * H + head) * maps + head % maps) * dk : q_out + ((size_t)t * H + head) * dk;
     } else {
         const int pi = pos / kv.page_size, off = pos - pi * kv.page_size;
         const int page = (ok && pi < kv.max_pages) ? kv.page_table[(size_t)slot * kv.max_pages + pi] : -1;
@@ -129,7 +131,8 @@ qkv_prepare_kernel(const void* __restrict__ src, int S, size_t slice, int width,
 // k_off (G heads of dk), v at v_off (G heads of dv).  table (or null: no rotation): float32 [table_len][rot_dims/2][2].
 // q_norm / k_norm (or null): [dk] of type w_dt, or with NORM_WHOLE [H * dk] and [G * dk].  append = 0: only q is produced.
 // norm_opts: NORM_WHOLE | NORM_BARE (a per-head norm also where no weight is given) | NORM_LAST (the per-head norm follows
-// the rotation).  maps >= 1: H and G count heads; q_out is [T, H * maps, dk], key rows of the cache hold maps * dk numbers.
+// the rotation) | Q_SPREAD (q_out is [T, H * maps, maps * dk], zeroed by the caller; query j is written at columns
+// (j mod maps) * dk of row j).  maps >= 1: H and G count heads; q_out is [T, H * maps, dk], key rows of the cache hold maps * dk numbers.
 GFB_API int gfb_qkv_prepare(const void* src, int n_partials, int width, int q_off, int k_off, int v_off, void* q_out, int dt,
                             void* k_pool, void* v_pool, const int* page_table, int max_pages, int page_size, int n_pages,
                             const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths, int n_seqs,

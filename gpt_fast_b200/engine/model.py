@@ -191,6 +191,7 @@ class Transformer:
         `want_rows` (int32 [W]); None wants every row.  Appends this step's keys
         and values to the cache; the caller advances the lengths afterwards."""
         T = batch.n_tokens
+        ops.set_launch_overlap(self.spec.launch_overlap)
         x = torch.empty(T, self.dim, dtype=torch.float32, device=self.device)
         scale = 1.0 if self.spec.embed_scale is None else float(self.spec.embed_scale)
         if self.embedding is None:

@@ -67,6 +67,14 @@ def trace_times(records):
     return [(label, start.elapsed_time(stop)) for label, start, stop in records]
 
 
+def set_launch_overlap(on: bool) -> None:
+    """Whether kernels launched from now on may start while their predecessor in the stream still drains (the default), or
+    run strictly one after the other.  A model asks for the second through `ModelSpec.launch_overlap = False`."""
+    k = kernels()
+    if hasattr(k, "set_launch_overlap"):
+        k.set_launch_overlap(on)
+
+
 def new_status(device) -> torch.Tensor:
     return torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
 
@@ -221,7 +229,7 @@ def gated_norm(y, gate, gate_off: int, weight, out, group: int, eps: float, act:
 def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, n_kv: int, head_dim: int,
                 v_head_dim: int, table=None, rot_dims: int = 0, pairing: str = "half", q_norm=None, k_norm=None,
                 norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True, norm_whole: bool = False,
-                norm_bare: bool = False, norm_last: bool = False, maps: int = 1):
+                norm_bare: bool = False, norm_last: bool = False, maps: int = 1, q_spread: bool = False):
     """From a projection's row to attention's inputs.  src [T, W] holds q (H heads of head_dim), k (G heads of
     head_dim) and v (G heads of v_head_dim) at the column offsets `offsets` = (q, k, v); with `partials` (float32
     [S, T, W]) src is their sum.  Per head, in this order: root-mean-square norm of q and k with the weights
@@ -231,7 +239,12 @@ def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_
     weights are [H * head_dim] and [G * head_dim].  norm_bare: q and k are divided by their root mean square per head
     without a weight.  norm_last: the per-head norm follows the rotation.  maps > 1: every query head and every key head
     is `maps` vectors of head_dim side by side, each normed and rotated like a head; q_out is [T, H * maps, head_dim]
-    and a cached key row holds maps * head_dim numbers."""
+    and a cached key row holds maps * head_dim numbers.  q_spread (see `spread_queries`): q_out is [T, H * maps,
+    maps * head_dim], zeroed by the caller, and query j goes to columns (j mod maps) * head_dim of its row."""
+    if q_spread:
+        return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
+                                     rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append, norm_whole=norm_whole,
+                                     norm_bare=norm_bare, norm_last=norm_last, maps=maps, q_spread=True)
     if norm_bare or norm_last or maps != 1:
         return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
                                      rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append, norm_whole=norm_whole,
@@ -241,6 +254,15 @@ def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_
                                      rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append)
     return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
                                  rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append, norm_whole=True)
+
+
+def spread_queries(dtype, n_head: int, n_kv: int, head_dim: int, v_head_dim: int, maps: int, page_size: int) -> bool:
+    """Whether `attention` with `maps` score maps per head wants its queries spread out (`qkv_prepare(q_spread=True)`):
+    q [T, H * maps, maps * head_dim] with query j at columns (j mod maps) * head_dim of its row and zeros elsewhere, so that
+    against a cached row of `maps` keys side by side it meets its own key only.  The kernels decide: where their fast
+    attention takes heads of maps * head_dim, every map runs as an ordinary head."""
+    ask = getattr(kernels(), "spread_queries", None)
+    return bool(ask and ask(dtype, n_head, n_kv, head_dim, v_head_dim, maps, page_size))
 
 
 def retention(src, offsets, state, out, batch: BatchMeta, n_head: int, head_dim: int, v_head_dim: int, decay, table=None,
@@ -358,7 +380,8 @@ def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, hea
     softcap: the scaled score s becomes softcap * tanh(s / softcap).  keep_first (with a window): the sequence's first
     keep_first positions stay visible beyond the window.  maps = 2 with diff = (lambda, eps, out_scale): q is [T, H * 2, d],
     a cached key row holds two keys; each (query, key) pair is a softmax of its own over the same values, and the head's
-    output is (o_1 - lambda o_2) / sqrt(mean((o_1 - lambda o_2)^2) + eps) * out_scale."""
+    output is (o_1 - lambda o_2) / sqrt(mean((o_1 - lambda o_2)^2) + eps) * out_scale.  q may come spread out
+    ([T, H * 2, 2 d], see `spread_queries`)."""
     if softcap or keep_first or maps != 1:
         return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
                                    values_in_keys=values_in_keys, bias=bias, slopes=slopes, softcap=softcap, keep_first=keep_first,

@@ -82,17 +82,30 @@ class CudaKernels:
         self.trace = None                  # a list: (label, start event, stop event) of every launch is appended
         self._label = None                 # what the next launch is called in the trace (default: the entry point)
         self._bias_cache = {}              # distance biases in the tensor-core prefill kernel's layout, by table
+        self._overlap = True               # kernels may start while their predecessor drains (programmatic dependent launch)
 
     def _f(self, lib: str, name: str):
         key = (lib, name)
         fn = self._fn.get(key)
         if fn is None:
             handle = build.library(lib)
+            if not self._overlap:
+                handle.gfb_set_overlap(0)
             fn = getattr(handle, name)
             fn.restype = c_int
             self._fn[key] = fn
             fn._lib = handle
         return fn
+
+    def set_launch_overlap(self, on: bool) -> None:
+        """Whether the kernels launched from now on may start while their predecessor in the stream still drains.  Off: every
+        launch waits for the one before it in the ordinary way."""
+        on = bool(on)
+        if on == self._overlap:
+            return
+        self._overlap = on
+        for handle in {fn._lib for fn in self._fn.values()}:
+            handle.gfb_set_overlap(1 if on else 0)
 
     def _call(self, lib, name, *args):
         fn = self._f(lib, name)
@@ -436,7 +449,7 @@ class CudaKernels:
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
                     pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True, norm_whole=False,
-                    norm_bare=False, norm_last=False, maps=1):
+                    norm_bare=False, norm_last=False, maps=1, q_spread=False):
         T = batch.n_tokens
         if norm_whole and (norm_bare or norm_last or maps != 1):
             _fail("a norm over the whole projection has weights, runs ahead of the rotation and knows one map per head")
@@ -452,7 +465,7 @@ class CudaKernels:
         ends = [q_off + n_head * maps * head_dim] + ([k_off + n_kv * maps * head_dim, v_off + n_kv * v_head_dim] if append else [])
         if max(ends) > W:
             _fail(f"q, k and v at {offsets} do not fit rows of {W}")
-        _need(q_out, shape=(T, n_head * maps, head_dim), name="q_out")
+        _need(q_out, shape=(T, n_head * maps, head_dim * (maps if q_spread else 1)), name="q_out")
         if table is not None:
             _need(table, torch.float32, name="rotary table")
             if table.shape[1] * 2 != rot_dims:
@@ -474,7 +487,7 @@ class CudaKernels:
                    c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
                    c_int(_PAIRING[pairing]), _ptr(q_norm), _ptr(k_norm), c_int(w_dt), c_float(norm_eps), c_float(k_scale),
                    c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(v_head_dim), c_int(1 if append else 0),
-                   c_int((1 if norm_whole else 0) | (2 if norm_bare else 0) | (4 if norm_last else 0)), c_int(maps),
+                   c_int((1 if norm_whole else 0) | (2 if norm_bare else 0) | (4 if norm_last else 0) | (8 if q_spread else 0)), c_int(maps),
                    _ptr(batch.status), _stream())
 
     def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
@@ -731,10 +744,27 @@ class CudaKernels:
         return None
 
     # -- attention ---------------------------------------------------------------------
+    def spread_queries(self, dtype, n_head, n_kv, head_dim, v_head_dim, maps, page_size) -> bool:
+        """Whether attention with `maps` score maps per head wants its queries spread out: q [T, H * maps, maps * head_dim] with
+        query j at columns (j mod maps) * head_dim of its row and zeros elsewhere.  Against the cached row of `maps` keys
+        side by side such a query meets its own key only, so every map is an ordinary head of maps * head_dim and the
+        tensor-core kernels run as they are."""
+        d = maps * head_dim
+        return (dtype == torch.bfloat16 and maps > 1 and d == v_head_dim and d in (64, 128) and page_size == 64
+                and (n_head * maps) // n_kv <= 8)
+
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
                   values_in_keys=False, bias=None, slopes=None, softcap=None, keep_first=0, maps=1, diff=None):
         T = batch.n_tokens
         dv = v_head_dim or head_dim
+        if maps == 2 and diff is not None and q.dim() == 3 and q.shape[2] == maps * head_dim:
+            # spread queries: 2H ordinary heads over the same keys and values, then the difference of each pair of maps
+            both = torch.empty(T, n_head * maps * dv, dtype=q.dtype, device=q.device)
+            self.attention(q, kv, batch, both, n_head * maps, n_kv, maps * head_dim, scale, window, chunk, sink, dv, values_in_keys,
+                           bias, slopes, softcap, keep_first)
+            _need(out, q.dtype, (T, n_head * dv), "attention output")
+            return self._call("elementwise", "gfb_diff_combine", _ptr(both), _ptr(out), c_int(_dt(out)), c_int(T), c_int(n_head), c_int(dv),
+                              c_float(diff[0]), c_float(diff[1]), c_float(diff[2]), _stream())
         if maps not in (1, 2) or (maps == 2) != (diff is not None):
             _fail("two score maps per head come with (lambda, eps, out_scale), one map without")
         if keep_first and not window:
@@ -749,7 +779,8 @@ class CudaKernels:
         if slopes is not None:
             _need(slopes, torch.float32, (n_head,), "distance slopes")
         biased = bias is not None or slopes is not None
-        special = bool(softcap) or bool(keep_first) or maps != 1      # what only the generic kernel has
+        capped = bool(softcap) or bool(keep_first)                    # the tensor-core kernels have these at head sizes 64 and 128
+        special = capped or maps != 1
         plain = chunk is None and sink is None and not biased and not special
         if (values_in_keys and not biased and not special and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
                 and not window and head_dim % 16 == 0 and dv % 16 == 0 and dv <= 512 and dv < head_dim and kv.page_size % 32 == 0
@@ -768,11 +799,13 @@ class CudaKernels:
                               c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
                               c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), c_int(splits),
                               _ptr(scratch), _ptr(batch.status), _stream())
-        if (not values_in_keys and not special and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
-                and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256)) and (not biased or scale > 0)):
-            # the tensor-core kernels; a block mask, a sink or a distance bias only at the head sizes they are built for
+        if (not values_in_keys and maps == 1 and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+                and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256)) and (not (biased or capped) or scale > 0)
+                and not (keep_first and (biased or sink is not None))):
+            # the tensor-core kernels; a block mask, a sink, a distance bias, a soft cap or kept first positions only at the
+            # head sizes they are built for
             return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink,
-                                        bias=bias, slopes=slopes)
+                                        bias=bias, slopes=slopes, softcap=softcap, keep_first=keep_first)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
                    c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), c_int(1 if values_in_keys else 0),
@@ -810,11 +843,21 @@ class CudaKernels:
         return arrays, length, top, per_head
 
     def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0,
-                        max_blocks=0, chunk=None, sink=None, bias=None, slopes=None):
+                        max_blocks=0, chunk=None, sink=None, bias=None, slopes=None, softcap=None, keep_first=0):
         T = batch.n_tokens
+        capped = bool(softcap) or bool(keep_first)
         if prefill is None:
             prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
         if prefill and head_dim in (64, 128) and n_head // n_kv <= 8:
+            if capped:
+                arrays, length, top, per_head = self._distance_arrays(bias, slopes, scale) if (bias is not None or slopes is not None) else (None, 0, 0, None)
+                # kept first positions are merged into the rows behind the windowed attention, which leaves each row's log-sum-exp
+                lse = torch.empty(T * n_head, dtype=torch.float32, device=q.device) if keep_first else None
+                self._call("attention_tc", "gfb_attn_prefill_tc_capped", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                           c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0),
+                           _ptr(sink), _ptr(arrays), c_int(length), c_int(top), _ptr(per_head), c_float(softcap or 0.0),
+                           c_int(int(keep_first or 0)), _ptr(lse), c_int(tiles), c_int(max_blocks), _ptr(batch.status), _stream())
+                return
             if bias is not None or slopes is not None:
                 arrays, length, top, per_head = self._distance_arrays(bias, slopes, scale)
                 self._call("attention_tc", "gfb_attn_prefill_tc_biased", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
@@ -831,10 +874,20 @@ class CudaKernels:
             if batch.max_q_len == 1:
                 # a query reads at most its own block of `chunk` positions (and the page that block starts in)
                 reach = batch.max_kv_len if not chunk else min(batch.max_kv_len, chunk + kv.page_size)
+                if window and capped:
+                    reach = min(reach, window + kv.page_size)   # the window's slices; the kept first positions have their own
                 splits = self.decode_slices(reach, kv.page_size, T * n_kv)
+            if keep_first:
+                splits += 1                                 # the kept first positions are a slice of their own, the grid's last
         scratch = None
         if splits > 1:
             scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+        if capped:
+            self._call("attention_bf16", "gfb_attn_decode_capped", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
+                       _ptr(bias), c_int(bias.shape[0] if bias is not None else 0), _ptr(slopes), c_float(softcap or 0.0),
+                       c_int(int(keep_first or 0)), c_int(splits), _ptr(scratch), _ptr(batch.status), _stream())
+            return
         if bias is not None or slopes is not None:
             self._call("attention_bf16", "gfb_attn_decode_biased", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
                        c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),

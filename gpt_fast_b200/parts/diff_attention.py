@@ -85,12 +85,16 @@ class DiffAttention:
             raise ValueError("a differential attention layer without key/value projections reads another run's cache entry")
         qkv = torch.empty(T, self.wqkv.shape[0], dtype=self.dtype, device=h.device)
         partials = ops.linear(h, self.wqkv, qkv, defer=True)
-        q = torch.empty(T, H * MAPS, d, dtype=self.dtype, device=h.device)
+        # where the kernels' fast attention takes heads of 2 d, every map runs as an ordinary head: its query lies in the
+        # columns of its own key and zeros face the other map's
+        spread = ops.spread_queries(self.dtype, H, G, d, dv, MAPS, view.kv.page_size)
+        q = (torch.zeros(T, H * MAPS, MAPS * d, dtype=self.dtype, device=h.device) if spread
+             else torch.empty(T, H * MAPS, d, dtype=self.dtype, device=h.device))
         pos = self.position
         ops.qkv_prepare(qkv, partials, (0, H * MAPS * d, (H + G) * MAPS * d), q, view.kv, batch, H, G, d, dv,
                         table=None if pos is None else pos.table, rot_dims=0 if pos is None else pos.head_dim,
                         pairing="half" if pos is None else pos.pairing, q_norm=self.q_norm, k_norm=self.k_norm,
-                        norm_eps=self.eps, append=append, maps=MAPS)
+                        norm_eps=self.eps, append=append, maps=MAPS, **({"q_spread": True} if spread else {}))
         y = torch.empty(T, H * dv, dtype=self.dtype, device=h.device)
         ops.attention(q, view.kv, batch, y, H, G, d, self.scale, v_head_dim=dv, maps=MAPS, diff=(self.lam, self.eps, 1.0 - self.diff))
         as_residual(residual).add_linear(y, self.wo)

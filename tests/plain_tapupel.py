@@ -189,9 +189,14 @@ def router_choice(z, top):
     return idx, torch.softmax(z.gather(1, idx), -1)
 
 
-def experts(x, mlp, w):
+def experts(x, mlp, w, margins=None):
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
-    idx, wt = router_choice(x @ w["router"].T, top)
+    z = x @ w["router"].T
+    idx, wt = router_choice(z, top)
+    if margins is not None:
+        # how far the last chosen logit lies above the first one left out, per token (infinite where all are chosen)
+        zs = z.sort(-1, descending=True).values
+        margins.append(zs[:, top - 1] - zs[:, top] if top < E else torch.full((x.shape[0],), math.inf, dtype=F64))
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for r in range(top):
@@ -207,8 +212,9 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: v.to(F64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, streams=None):
-    """Logits [T, vocab] (64-bit) of one whole sequence; `streams` (a list) receives x behind every layer."""
+def forward(cfg, tensors, tokens, streams=None, margins=None):
+    """Logits [T, vocab] (64-bit) of one whole sequence; `streams` (a list) receives x behind every layer, `margins` (a
+    list) the router's margin per token of every layer with experts."""
     eps = cfg["norm"]["eps"]
     x = tensors["embed"].to(F64)[torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
     kept = {}
@@ -227,7 +233,7 @@ def forward(cfg, tensors, tokens, streams=None):
         x = x + one_plus_norm(y, tensors[f"l{i}.norm1"].to(F64), eps)
         if L.get("mlp"):
             w = sub(tensors, f"l{i}.mlp.")
-            y = gated_ff(x, w) if L["mlp"]["kind"] == "dense" else experts(x, L["mlp"], w)
+            y = gated_ff(x, w) if L["mlp"]["kind"] == "dense" else experts(x, L["mlp"], w, margins)
             x = x + one_plus_norm(y, tensors[f"l{i}.norm2"].to(F64), eps)
         if streams is not None:
             streams.append(x.clone())
