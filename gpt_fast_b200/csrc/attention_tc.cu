@@ -1112,54 +1112,60 @@ GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, v
 // the first positions it does not see (j < min(keep_first, first key of its window)) into its row: with the row's log-sum-exp
 // L (log2 units) from the attention kernel and x_j = log2(e) cap(scale q.k_j),
 //     M = max(L, max_j x_j),  w = 2^(L - M),  out <- (w out + sum_j 2^(x_j - M) v_j) / (w + sum_j 2^(x_j - M)).
-// One block per (token, head); the kept positions are few.
+// One warp per (token, head), a lane holds DH / 32 dimensions of the row; the kept positions are few.
 template <int DH>
-__global__ void __launch_bounds__(DH)
+__global__ void __launch_bounds__(128)
 attn_kept_merge_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const float* __restrict__ lse,
                        const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                        const int* __restrict__ page_table, int max_pages, int n_pages, GfbBatch b, int H, int G, float scale,
                        float softcap, int window, int keep_first, int* status) {
-    __shared__ float red[DH / 32];
+    constexpr int PER = DH / 32;
     gfb_pdl_launch();
     gfb_pdl_wait();
-    const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long)b.n_tokens * H) return;
+    const int t = (int)(item / H), h = (int)(item - (long)t * H);
     const int s = b.tok_seq[t];
     const int slot = b.slots[s];
     const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
-    const int lo = pos - window + 1;
-    const int kept = min(keep_first, lo);
+    const int kept = min(keep_first, pos - window + 1);
     if (kept <= 0) return;
     const int g = h / (H / G);
-    const float qi = __bfloat162float(q[((size_t)t * H + h) * DH + i]);
-    const size_t at = ((size_t)t * H + h) * DH + i;
-    float m = lse[(size_t)t * H + h], den = 1.f, acc = __bfloat162float(out[at]);    // in units of 2^m
-    if (m == -INFINITY) { den = 0.f; acc = 0.f; }
+    const size_t at = (size_t)item * DH + lane * PER;
+    float qv[PER], acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) { qv[i] = __bfloat162float(q[at + i]); acc[i] = __bfloat162float(out[at + i]); }
+    float m = lse[item], den = 1.f;                              // the row so far, in units of 2^m
+    if (m == -INFINITY) {
+        den = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] = 0.f;
+    }
     for (int j = 0; j < kept; j++) {
         const int pi = j / PAGE;
         const int page = pi < max_pages ? page_table[(size_t)slot * max_pages + pi] : -1;
         if (page < 0 || page >= n_pages) {
-            if (i == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi);
+            if (lane == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi);
             return;
         }
-        const size_t row = (((size_t)page * G + g) * PAGE + (j - pi * PAGE)) * DH + i;
-        float dot = qi * __bfloat162float(k_pool[row]);
-        dot = gfb_warp_sum(dot);
-        __syncthreads();                                       // red is free again
-        if ((i & 31) == 0) red[i >> 5] = dot;
-        __syncthreads();
-        float sc = 0.f;
+        const size_t row = (((size_t)page * G + g) * PAGE + (j - pi * PAGE)) * DH + lane * PER;
+        float dot = 0.f;
 #pragma unroll
-        for (int w = 0; w < DH / 32; w++) sc += red[w];
-        sc *= scale;
+        for (int i = 0; i < PER; i++) dot = fmaf(qv[i], __bfloat162float(k_pool[row + i]), dot);
+        float sc = gfb_warp_sum(dot) * scale;
         if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
         const float x = sc * 1.4426950408889634f;
         const float m_new = fmaxf(m, x);
         const float down = m == -INFINITY ? 0.f : exp2f(m - m_new), p = exp2f(x - m_new);
         den = den * down + p;
-        acc = acc * down + p * __bfloat162float(v_pool[row]);
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] = acc[i] * down + p * __bfloat162float(v_pool[row + i]);
         m = m_new;
     }
-    out[at] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) out[at + i] = __float2bfloat16_rn(acc[i] * inv);
 }
 
 // The same with a bias by head and distance in units of the raw score (the bias divided by `scale`): `bias` null or
@@ -1296,14 +1302,13 @@ GFB_API int gfb_attn_prefill_tc_capped(const void* q, void* out, void* k_pool, v
     }
     if (gfb_check(e, "gfb_attn_prefill_tc")) return 1;
     if (keep_first > 0) {
-        if (H > 65535) return gfb_fail("gfb_attn_prefill_tc: %d heads exceed the grid limit", H);
-        const dim3 grid(n_tokens, H);
+        const dim3 grid((unsigned)(((long)n_tokens * H + 3) / 4));
         if (d == 128)
             e = gfb_launch(attn_kept_merge_kernel<128>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const float*)lse,
                            (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages, n_pages, b, H, G, scale, softcap,
                            window, keep_first, status);
         else
-            e = gfb_launch(attn_kept_merge_kernel<64>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const float*)lse,
+            e = gfb_launch(attn_kept_merge_kernel<64>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const float*)lse,
                            (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages, n_pages, b, H, G, scale, softcap,
                            window, keep_first, status);
         return gfb_check(e, "gfb_attn_prefill_tc (kept first positions)");

@@ -194,9 +194,10 @@ def experts(x, mlp, w, margins=None):
     z = x @ w["router"].T
     idx, wt = router_choice(z, top)
     if margins is not None:
-        # how far the last chosen logit lies above the first one left out, per token (infinite where all are chosen)
+        # how far the last chosen logit lies above the first one left out, per token, in units of the spread of the token's
+        # logits (infinite where all are chosen)
         zs = z.sort(-1, descending=True).values
-        margins.append(zs[:, top - 1] - zs[:, top] if top < E else torch.full((x.shape[0],), math.inf, dtype=F64))
+        margins.append((zs[:, top - 1] - zs[:, top]) / (z.std(-1) + 1e-30) if top < E else torch.full((x.shape[0],), math.inf, dtype=F64))
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for r in range(top):
