@@ -597,7 +597,7 @@ GFB_API int gfb_gated_norm(const float* y, const void* gate, int gate_dt, int ld
 // output channel of the block for both gates: per input one weight of each gate (the matrices are stored [block][in][out], so a
 // warp reads consecutive outputs) against the tile's tokens.  It leaves a and b = sqrt(1 - a^2) i u per token and channel.
 // Then the recurrence: a thread per (sequence, channel) walks through the sequence's tokens of this step, S <- a S + b, and writes
-// S gelu_tanh(y + by).  A number's sums do not depend on how the sequence was cut or batched.
+// S gelu_tanh(y + by); a step with more than 64 tokens of a sequence walks in chunks side by side (below).
 constexpr int RG_TOKENS = 16;
 constexpr int RG_THREADS = 128;
 
@@ -690,13 +690,108 @@ rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ bb, con
     *st = S;
 }
 
+// Prompts: the same recurrence in chunks of RG_CHUNK tokens, which all run side by side.  S <- a S + b is a composition of
+// affine maps, so a chunk is summed up as (P, Q) = (product of its a, its end state from zero); a short walk over a sequence's
+// chunks gives every chunk the state it starts from (and the sequence its new state); then every chunk walks its tokens from there.
+constexpr int RG_CHUNK = 64;
+
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_chunk_kernel(const float* __restrict__ a, const float* __restrict__ bb, float* __restrict__ P, float* __restrict__ Q, GfbBatch b,
+                   int C, int max_chunks) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.x, k = blockIdx.y;
+    const int c = blockIdx.z * RG_THREADS + threadIdx.x;
+    const int t0 = b.cu_seqlens[s], n = b.cu_seqlens[s + 1] - t0;
+    if (c >= C || k * RG_CHUNK >= n) return;
+    const int first = t0 + k * RG_CHUNK, count = min(RG_CHUNK, n - k * RG_CHUNK);
+    float prod = 1.f, end = 0.f;
+    constexpr int U = 8;
+    for (int i0 = 0; i0 < count; i0 += U) {
+        float av[U], bv[U];
+#pragma unroll
+        for (int j = 0; j < U; j++) {
+            const int t = first + min(i0 + j, count - 1);
+            av[j] = a[(size_t)t * C + c];
+            bv[j] = bb[(size_t)t * C + c];
+        }
+#pragma unroll
+        for (int j = 0; j < U; j++)
+            if (i0 + j < count) { prod *= av[j]; end = fmaf(av[j], end, bv[j]); }
+    }
+    const size_t at = ((size_t)s * max_chunks + k) * C + c;
+    P[at] = prod;
+    Q[at] = end;
+}
+
+// P is overwritten by the state every chunk starts from
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_carry_kernel(float* __restrict__ P, const float* __restrict__ Q, float* __restrict__ state, size_t state_ld, GfbBatch b, int C,
+                   int max_chunks) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * RG_THREADS + threadIdx.x;
+    if (c >= C) return;
+    const int n = b.cu_seqlens[s + 1] - b.cu_seqlens[s];
+    const int chunks = (n + RG_CHUNK - 1) / RG_CHUNK;
+    float* st = state + (size_t)b.slots[s] * state_ld + c;
+    float S = *st;
+    for (int k = 0; k < chunks; k++) {
+        const size_t at = ((size_t)s * max_chunks + k) * C + c;
+        const float p = P[at];
+        P[at] = S;
+        S = fmaf(p, S, Q[at]);
+    }
+    *st = S;
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_apply_kernel(const float* __restrict__ a, const float* __restrict__ bb, const float* __restrict__ start, const TY* __restrict__ y,
+                   int ld_y, int y_off, const void* __restrict__ y_bias, int v_dt, TO* __restrict__ out, GfbBatch b, int C, int max_chunks) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.x, k = blockIdx.y;
+    const int c = blockIdx.z * RG_THREADS + threadIdx.x;
+    const int t0 = b.cu_seqlens[s], n = b.cu_seqlens[s + 1] - t0;
+    if (c >= C || k * RG_CHUNK >= n) return;
+    const int first = t0 + k * RG_CHUNK, count = min(RG_CHUNK, n - k * RG_CHUNK);
+    const float yb = y_bias != nullptr ? ldw(y_bias, v_dt, c) : 0.f;
+    float S = start[((size_t)s * max_chunks + k) * C + c];
+    constexpr int U = 8;
+    for (int i0 = 0; i0 < count; i0 += U) {
+        float av[U], bv[U], yv[U];
+#pragma unroll
+        for (int j = 0; j < U; j++) {
+            const int t = first + min(i0 + j, count - 1);
+            av[j] = a[(size_t)t * C + c];
+            bv[j] = bb[(size_t)t * C + c];
+            yv[j] = gfb_to_f32(y[(size_t)t * ld_y + y_off + c]);
+        }
+#pragma unroll
+        for (int j = 0; j < U; j++)
+            if (i0 + j < count) {
+                S = fmaf(av[j], S, bv[j]);
+                out[(size_t)(first + i0 + j) * C + c] = gfb_from_f32<TO>(S * gelu_tanh_f(yv[j] + yb));
+            }
+    }
+}
+
 // u float32 [T, C]: the recurrence's inputs.  wa, wi [blocks][C / blocks (in)][C / blocks (out)] of type w_dt: the two gates'
 // matrices, transposed per block.  ba, bi, lam, y_bias [C] of type v_dt.  y [T, ld_y] of type y_dt, its C columns from y_off.
-// state float32, slot stride state_ld, C numbers per slot.  out [T, C] of type out_dt.  scratch float32 [2][T][C].
+// state float32, slot stride state_ld, C numbers per slot.  out [T, C] of type out_dt.  scratch float32 [2][T][C], and behind it,
+// where the longest sequence of the step (max_q_len) has more than one chunk of 64 tokens, [2][n_seqs][chunks of max_q_len][C].
+GFB_API long gfb_rglru_scratch_floats(int n_tokens, int n_seqs, int max_q_len, int C) {
+    long need = 2L * n_tokens * C;
+    if (max_q_len > RG_CHUNK) need += 2L * n_seqs * ((max_q_len + RG_CHUNK - 1) / RG_CHUNK) * C;
+    return need;
+}
+
 GFB_API int gfb_rglru(const float* u, const void* wa, const void* wi, int w_dt, const void* ba, const void* bi, const void* lam,
                       const void* y_bias, int v_dt, float decay_scale, const void* y, int y_dt, int ld_y, int y_off, float* state,
                       long state_ld, void* out, int out_dt, float* scratch, const int* cu_seqlens, const int* tok_seq, const int* slots,
-                      const int* lengths, int n_seqs, int n_tokens, int C, int blocks, cudaStream_t stream) {
+                      const int* lengths, int n_seqs, int n_tokens, int max_q_len, int C, int blocks, cudaStream_t stream) {
     if (n_tokens <= 0 || C <= 0) return 0;
     if (blocks < 1 || C % blocks) return gfb_fail("gfb_rglru: %d channels do not divide into %d blocks", C, blocks);
     const int bw = C / blocks;
@@ -725,6 +820,25 @@ GFB_API int gfb_rglru(const float* u, const void* wa, const void* wi, int w_dt, 
     if (gfb_check(e, "gfb_rglru (gates)")) return 1;
     const dim3 sgrid(n_seqs, (C + RG_THREADS - 1) / RG_THREADS);
     typedef __nv_bfloat16 bf16;
+    if (max_q_len > RG_CHUNK) {
+        const int max_chunks = (max_q_len + RG_CHUNK - 1) / RG_CHUNK;
+        if (max_chunks > 65535) return gfb_fail("gfb_rglru: a step of %d tokens of one sequence", max_q_len);
+        float* P = b_buf + (size_t)n_tokens * C;
+        float* Q = P + (size_t)n_seqs * max_chunks * C;
+        const dim3 cgrid(n_seqs, max_chunks, (C + RG_THREADS - 1) / RG_THREADS);
+        e = gfb_launch(rglru_chunk_kernel, cgrid, dim3(RG_THREADS), 0, stream, (const float*)a_buf, (const float*)b_buf, P, Q, b, C, max_chunks);
+        if (gfb_check(e, "gfb_rglru (chunks)")) return 1;
+        e = gfb_launch(rglru_carry_kernel, sgrid, dim3(RG_THREADS), 0, stream, P, (const float*)Q, state, (size_t)state_ld, b, C, max_chunks);
+        if (gfb_check(e, "gfb_rglru (carry)")) return 1;
+#define APPLY(TY, TO) e = gfb_launch(rglru_apply_kernel<TY, TO>, cgrid, dim3(RG_THREADS), 0, stream, (const float*)a_buf, (const float*)b_buf, \
+                                     (const float*)P, (const TY*)y, ld_y, y_off, y_bias, v_dt, (TO*)out, b, C, max_chunks)
+        if (y_dt == GFB_BF16 && out_dt == GFB_BF16) APPLY(bf16, bf16);
+        else if (y_dt == GFB_F32 && out_dt == GFB_F32) APPLY(float, float);
+        else if (y_dt == GFB_F32 && out_dt == GFB_BF16) APPLY(float, bf16);
+        else return gfb_fail("gfb_rglru: unsupported types y %d out %d", y_dt, out_dt);
+#undef APPLY
+        return gfb_check(e, "gfb_rglru (apply)");
+    }
 #define SCAN(TY, TO) e = gfb_launch(rglru_scan_kernel<TY, TO>, sgrid, dim3(RG_THREADS), 0, stream, (const float*)a_buf, (const float*)b_buf, \
                                     (const TY*)y, ld_y, y_off, y_bias, v_dt, state, (size_t)state_ld, (TO*)out, b, C)
     if (y_dt == GFB_BF16 && out_dt == GFB_BF16) SCAN(bf16, bf16);

@@ -389,10 +389,15 @@ class CudaKernels:
             _fail(f"{C} columns at {y_off} do not fit {tuple(y_src.shape)}")
         _need(out, shape=(T, C), name="recurrence output")
         sp, sld = self._state_args(state, state_off, C)
-        scratch = torch.empty(2, T, C, dtype=torch.float32, device=u.device)
+        fn = self._f("recurrent", "gfb_rglru_scratch_floats")
+        fn.restype = c_long
+        need = fn(c_int(T), c_int(batch.n_seqs), c_int(int(batch.max_q_len)), c_int(C))
+        fn.restype = c_int
+        scratch = torch.empty(need, dtype=torch.float32, device=u.device)
         self._call("recurrent", "gfb_rglru", _ptr(u), _ptr(w_a), _ptr(w_i), c_int(_dt(w_a)), _ptr(b_a), _ptr(b_i), _ptr(lam), _ptr(y_bias),
                    c_int(_dt(b_a)), c_float(decay_scale), _ptr(y_src), c_int(_dt(y_src)), c_int(y_src.shape[1]), c_int(y_off), sp, sld,
-                   _ptr(out), c_int(_dt(out)), _ptr(scratch), *self._batch_args(batch), c_int(C), c_int(blocks), _stream())
+                   _ptr(out), c_int(_dt(out)), _ptr(scratch), *self._batch_args(batch), c_int(int(batch.max_q_len)), c_int(C), c_int(blocks),
+                   _stream())
 
     def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
                  n_state, n_groups):
