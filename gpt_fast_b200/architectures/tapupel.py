@@ -86,7 +86,8 @@ def _rot(m: Dict[str, Any], where: str, dim: int) -> Dict[str, Any]:
 
 
 def _heads(m: Dict[str, Any], where: str) -> Dict[str, Any]:
-    out = {k: _int(m, k, where) for k in ("heads", "kv_heads", "dim", "vdim")}
+    out = {k: _int(m, k, where) for k in ("heads", "kv_heads", "dim")}
+    out["vdim"] = out["dim"] if m.get("vdim") is None else _int(m, "vdim", where)      # not given: as wide as the keys
     if out["heads"] % out["kv_heads"]:
         raise ConfigError(f"config.json: {where}{out['heads']} heads do not divide into {out['kv_heads']} kv_heads")
     out["scale"] = _num(m, "scale", where)
